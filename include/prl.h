@@ -739,6 +739,62 @@ int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_t a_mod, co
 int prl_moe_glu(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm, const float* wsel,
                 float limit, float beta, void* out, int32_t f32, prl_stream_t stream);
 
+/* ---- latent attention, delta-rule memory, multi-stream residual (csrc/latent_ops.cu, delta_scan.cu, stream_ops.cu) ---- */
+/* `batch` independent products C_b = A_b W_b^T in one launch; the *_batch strides are in elements */
+int prl_gemm_any_batched(const void* A, int32_t a_is_f32, int64_t lda, int64_t a_batch, const void* W, int32_t w_is_f32,
+                         int64_t ldw, int64_t w_batch, int64_t M, int64_t N, int64_t K, float* C, int64_t ldc,
+                         int64_t c_batch, int32_t batch, prl_stream_t stream);
+/* prl_attn_any_masked with a value row stride (v_pool may alias k_pool: values = leading channels of the key rows) and a
+ * per-head sink logit (NULL = none) that joins the softmax denominator only */
+int prl_attn_any_sink(const void* q, const void* k_pool, const void* v_pool, int32_t ldv, int32_t f32,
+                      const int32_t* block_table, int32_t max_blocks, int32_t page_size, const int32_t* seg_start,
+                      const int32_t* seg_len, const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q,
+                      int32_t H, int32_t G, int32_t dim, int32_t vdim, float scale, int32_t window, int32_t keep_first,
+                      float softcap, const float* sink, int32_t out_is_t, void* out, prl_stream_t stream);
+/* query latent cq = rmsnorm(P[off_q : off_q + q_rank]) * q_gain (operand type) and the latent cache row
+ * [rmsnorm(P[off_kv : +rank]) * kv_gain | rotate_half(P[off_kv + rank : +rot], pos)] -> pool[page][page_size][rank + rot] */
+int prl_latent_prep(const float* P, int64_t ldp, int32_t off_q, int32_t q_rank, int32_t off_kv, int32_t rank, int32_t rot,
+                    const double* freq, const float* q_gain, const float* kv_gain, float eps, const int32_t* row_pos,
+                    const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks, int32_t page_size, int32_t n,
+                    void* cq_out, void* pool, int32_t f32, prl_stream_t stream);
+/* per head [dim | rot] of Q: the unrotated parts -> q_plain [n][H*dim], the rotated part (rotate-half at the row's
+ * position) -> q_att[n][H][rank + rot] behind its first `rank` channels */
+int prl_latent_query(const float* Q, int64_t ldq, int32_t n, int32_t H, int32_t dim, int32_t rot, int32_t rank,
+                     const double* freq, const int32_t* row_pos, void* q_plain, void* q_att, int32_t f32,
+                     prl_stream_t stream);
+/* out[r][g][c] = T(src[r][g*C + c]), rows of out ld_out apart per group (G = 1: a cast of fp32 rows to the operand type) */
+int prl_store_groups(const float* src, int64_t lds, int32_t n, int32_t G, int32_t C, void* out, int64_t ld_out, int32_t f32,
+                     prl_stream_t stream);
+/* S_t = diag(w_t) S_(t-1) - (a_t u_t)(u_t^T S_(t-1)) + k_t v_t^T, o_t = S_t^T r_t;  u = k / sqrt(sum k^2 + unit_eps),
+ * w = exp(-decay_scale sigmoid(zw + w_bias)), a = sigmoid(P[off_a] + a_bias);  state [slot][head][dv][dk] fp32 */
+int64_t prl_delta_state_floats(int32_t heads, int32_t dk, int32_t dv);
+int prl_delta_scan(const float* P, int64_t ldp, int32_t off_r, int32_t off_k, int32_t off_v, int32_t off_a, const float* zw,
+                   int64_t ldw, const float* w_bias, const float* a_bias, float decay_scale, float unit_eps, int32_t heads,
+                   int32_t dk, int32_t dv, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                   int32_t n_seg, float* state, float* out, int64_t ld_out, prl_stream_t stream);
+/* x = embed[token] * scale + pair[(prev * mul_prev + token * mul_cur) mod buckets] (row `buckets` at position 0; pair NULL:
+ * no such table); all S streams of the row start as x; ha = T(tanh(alpha * sum_s w_in[s] x) * gain + shift) */
+int prl_embed_pair(const int32_t* tokens, const int32_t* row_pos, const int32_t* row_slot, const int32_t* row_back,
+                   const int32_t* prev_state, const void* embed, const void* pair, int32_t f32, float scale, int32_t buckets,
+                   int32_t mul_prev, int32_t mul_cur, int32_t n, int32_t W, int32_t vocab, int32_t S, const float* w_in,
+                   const float* alpha, const float* gain, const float* shift, float* xs, void* ha, prl_stream_t stream);
+/* prev_state[slot] = last token of every non-empty segment */
+int prl_last_token(const int32_t* tokens, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
+                   int32_t n_seg, int32_t* prev_state, prl_stream_t stream);
+/* ha[i] = T(tanh(alpha * sum_s w_in[s] xs[rows[i]][s]) * gain + shift)   (rows NULL = identity) */
+int prl_streams_open(const float* xs, const int32_t* rows, int32_t n_out, int32_t S, int32_t W, const float* w_in,
+                     const float* alpha, const float* gain, const float* shift, void* ha, int32_t f32, prl_stream_t stream);
+/* y = sum of n_split slices; y *= scale * sigmoid(gate + gate_bias) (each optional); xs'[t] = sum_s mix[s][t] xs[s] +
+ * w_out[t] y; then, if next_in is given, the next reader's ha as in prl_streams_open */
+int prl_streams_close(const float* y, int64_t ldy, int32_t n_split, int64_t split_stride, const float* scale,
+                      const float* gate, int64_t ldg, const float* gate_bias, const float* mix, const float* w_out, int32_t S,
+                      int32_t n, int32_t W, float* xs, const float* next_in, const float* next_alpha, const float* next_gain,
+                      const float* next_shift, void* ha, int32_t f32, prl_stream_t stream);
+/* out = silu(gate) * up * (wsel * wscale): the pair's weight on the expert's OUTPUT (folded in front of the linear second
+ * projection).  prl_moe_route / prl_moe_router take softmax_weights = 2 for a softmax over ALL experts */
+int prl_moe_glu_out(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm, const float* wsel,
+                    float wscale, void* out, int32_t f32, prl_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

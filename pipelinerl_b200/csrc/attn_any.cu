@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
                                                        const int32_t* __restrict__ seg_len, const int32_t* __restrict__ seg_pos0,
                                                        const int32_t* __restrict__ seg_slot, int H, int G, int dim, int vdim,
                                                        float scale, int window, int keep_first, float softcap,
-                                                       void* __restrict__ out_v) {
+                                                       int ldv, const float* __restrict__ sink, void* __restrict__ out_v) {
   pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
                 // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
   // RW consecutive query rows per warp (kWarpsPerCta * RW per CTA): a staged key tile is scored against all of them in
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
       const int j = i / vdim, d = i - j * vdim;
       const int kt = k0 + j;
       const int page = bt[kt / page_size], within = kt % page_size;
-      Vs[j * vdim + d] = cvt(v_pool[(((int64_t)page * G + g) * page_size + within) * vdim + d]);
+      Vs[j * vdim + d] = cvt(v_pool[(((int64_t)page * G + g) * page_size + within) * ldv + d]);
     }
     __syncthreads();
     // which of this warp's rows see anything of the tile (warp-uniform), and which key this lane scores for them
@@ -163,6 +163,13 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
   for (int r = 0; r < RW; ++r) {
     const int my_i = w_i0 + r;
     if (my_i >= len) continue;
+    if (sink) {                                      // a logit without key or value: it joins the denominator only
+      const float m_new = fmaxf(m[r], sink[h]);
+      const float corr = expf(m[r] - m_new);
+      l[r] = l[r] * corr + expf(sink[h] - m_new);
+#pragma unroll
+      for (int i = 0; i < VR; ++i) acc[r][i] *= corr;
+    }
     const float inv = 1.f / l[r];
 #pragma unroll
     for (int i = 0; i < VR; ++i) {
@@ -178,14 +185,15 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
 template <typename T, int VR, bool OUT_T, int RW>
 int launch_attn_rw(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                    const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                   int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, void* out, cudaStream_t st) {
+                   int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, int ldv, const float* sink,
+                   void* out, cudaStream_t st) {
   constexpr int kRows = kWarpsPerCta * RW;
   const size_t smem = ((size_t)kKeysPerTile * (dim + 1) + (size_t)kKeysPerTile * vdim + (size_t)kRows * dim) * sizeof(float);
   static SmemAttr attr = {};
   if (smem > 48 * 1024) PRL_CUDA(ensure_smem(attn_any_kernel<T, VR, OUT_T, RW>, (int)smem, attr));
   dim3 grid((max_q + kRows - 1) / kRows, H, n_seg);
   PRL_CUDA(launch_pdl((attn_any_kernel<T, VR, OUT_T, RW>), dim3(grid), dim3(256), (size_t)(smem), st, (const T*)q, (const T*)kp, (const T*)vp, bt, max_blocks, page_size, ss, sl,
-                      sp, sslot, H, G, dim, vdim, scale, window, keep_first, softcap, out));
+                      sp, sslot, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
@@ -194,12 +202,13 @@ int launch_attn_rw(const void* q, const void* kp, const void* vp, const int32_t*
 template <typename T, int VR, bool OUT_T>
 int launch_attn(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                 const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, void* out, cudaStream_t st) {
+                int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, int ldv, const float* sink,
+                void* out, cudaStream_t st) {
   if (max_q >= 64 && VR <= 4)
     return launch_attn_rw<T, VR, OUT_T, 4>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim,
-                                           scale, window, keep_first, softcap, out, st);
+                                           scale, window, keep_first, softcap, ldv, sink, out, st);
   return launch_attn_rw<T, VR, OUT_T, 1>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim,
-                                         scale, window, keep_first, softcap, out, st);
+                                         scale, window, keep_first, softcap, ldv, sink, out, st);
 }
 
 // ---- single-token segments (a decode step) ------------------------------------------------------------------------------
@@ -234,7 +243,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pool, const T* __restrict__ v_pool, const int32_t* __restrict__ block_table,
     int max_blocks, int page_size, const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
     const int32_t* __restrict__ seg_pos0, const int32_t* __restrict__ seg_slot, int H, int G, int dim, int vdim, float scale,
-    int window, int keep_first, float softcap, void* __restrict__ out_v) {
+    int window, int keep_first, float softcap, int ldv, const float* __restrict__ sink, void* __restrict__ out_v) {
   pdl_wait();
   extern __shared__ float sm[];
   const int seg = blockIdx.y;
@@ -335,7 +344,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
       for (int u = 0; u < KB; ++u) {
         const int kj = k0 + j0 + u;
         const bool on = seen_mask >> (j0 + u) & 1u;            // hidden keys are not read: their weight is zero anyway
-        const T* vr = v_pool + (((int64_t)bt[(on ? kj : k0) / page_size] * G + g) * page_size + (on ? kj : k0) % page_size) * vdim;
+        const T* vr = v_pool + (((int64_t)bt[(on ? kj : k0) / page_size] * G + g) * page_size + (on ? kj : k0) % page_size) * ldv;
 #pragma unroll
         for (int i = 0; i < VR; ++i) {
           const int c = lane + 32 * i;
@@ -365,9 +374,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
   __syncthreads();
   for (int i = threadIdx.x; i < nh * vdim; i += blockDim.x) {    // merge the warps' partial softmaxes, in warp order
     const int hh = i / vdim, c = i - hh * vdim;
-    float mx = -INFINITY;
+    float mx = sink ? sink[h0 + hh] : -INFINITY;
     for (int w = 0; w < kDecWarps; ++w) mx = fmaxf(mx, part[((int64_t)w * kDecHeads + hh) * pstride + vdim]);
-    float num = 0.f, den = 0.f;
+    float num = 0.f, den = sink ? expf(sink[h0 + hh] - mx) : 0.f;      // the sink logit: denominator only
     for (int w = 0; w < kDecWarps; ++w) {
       const float* pw = part + ((int64_t)w * kDecHeads + hh) * pstride;
       const float wgt = pw[vdim] == -INFINITY ? 0.f : expf(pw[vdim] - mx);
@@ -383,14 +392,15 @@ __global__ void __launch_bounds__(kDecWarps * 32) attn_decode_any_kernel(
 template <typename T, int VR, bool OUT_T>
 int launch_attn_decode(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                        const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int H, int G,
-                       int dim, int vdim, float scale, int window, int keep_first, float softcap, void* out, cudaStream_t st) {
+                       int dim, int vdim, float scale, int window, int keep_first, float softcap, int ldv, const float* sink,
+                       void* out, cudaStream_t st) {
   const size_t smem = ((size_t)kDecHeads * dim + (size_t)kDecWarps * kDecHeads * (vdim + 2)) * sizeof(float);
   static SmemAttr attr = {};
   if (smem > 48 * 1024) PRL_CUDA(ensure_smem(attn_decode_any_kernel<T, VR, OUT_T>, (int)smem, attr));
   const int groups = (H / G + kDecHeads - 1) / kDecHeads;
   PRL_CUDA(launch_pdl((attn_decode_any_kernel<T, VR, OUT_T>), dim3(G * groups, n_seg), dim3(kDecWarps * 32), smem, st, (const T*)q,
                       (const T*)kp, (const T*)vp, bt, max_blocks, page_size, ss, sl, sp, sslot, H, G, dim, vdim, scale, window,
-                      keep_first, softcap, out));
+                      keep_first, softcap, ldv, sink, out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
@@ -398,11 +408,12 @@ int launch_attn_decode(const void* q, const void* kp, const void* vp, const int3
 template <typename T>
 int dispatch_attn(int vr, const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                   const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                  int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, int out_is_t, void* out, cudaStream_t st) {
-#define PRL_ATTN(VR) (out_is_t ? launch_attn<T, VR, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out, st) \
-                               : launch_attn<T, VR, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out, st))
-#define PRL_ATTN_DEC(VR) (out_is_t ? launch_attn_decode<T, VR, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, H, G, dim, vdim, scale, window, keep_first, softcap, out, st) \
-                                   : launch_attn_decode<T, VR, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, H, G, dim, vdim, scale, window, keep_first, softcap, out, st))
+                  int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, int ldv, const float* sink, int out_is_t,
+                  void* out, cudaStream_t st) {
+#define PRL_ATTN(VR) (out_is_t ? launch_attn<T, VR, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out, st) \
+                               : launch_attn<T, VR, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out, st))
+#define PRL_ATTN_DEC(VR) (out_is_t ? launch_attn_decode<T, VR, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out, st) \
+                                   : launch_attn_decode<T, VR, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out, st))
   if (max_q == 1 && page_size % kKeysPerTile == 0) {          // every segment is one token (or empty): the decode kernel
     if (vr <= 1) return PRL_ATTN_DEC(1);
     if (vr <= 2) return PRL_ATTN_DEC(2);
@@ -432,7 +443,10 @@ static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, 
                          int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
                          const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
                          int32_t G, int32_t dim, int32_t vdim, float scale, int32_t window, int32_t keep_first,
-                         float softcap, int32_t out_is_t, void* out, prl_stream_t st) {
+                         float softcap, int32_t out_is_t, void* out, prl_stream_t st, int32_t ldv = 0,
+                         const float* sink = nullptr) {
+  if (ldv <= 0) ldv = vdim;
+  PRL_CHECK_ARG(ldv >= vdim, "prl_attn_any: value row stride %d below the value size %d", ldv, vdim);
   PRL_CHECK_ARG(q && k_pool && v_pool && block_table && seg_start && seg_len && seg_pos0 && seg_slot && out,
                 "prl_attn_any: NULL argument");
   PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && H <= 65535 && G >= 1 && H % G == 0 && dim >= 1 &&
@@ -440,13 +454,13 @@ static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, 
                 "prl_attn_any: bad shape (H=%d G=%d dim=%d vdim=%d; dim <= 512, vdim <= 256)", H, G, dim, vdim);
   PRL_CHECK_ARG(window >= 0 && keep_first >= 0 && softcap >= 0.f, "prl_attn_any: bad mask (window=%d keep_first=%d)", window, keep_first);
   const int vr = (vdim + 31) / 32;
-  if (!f32 && g_attn_tensor_cores && max_q >= kMmaMinRows && attn_mma_fits(dim, vdim, q, k_pool, v_pool))
+  if (!f32 && g_attn_tensor_cores && max_q >= kMmaMinRows && !sink && ldv == vdim && attn_mma_fits(dim, vdim, q, k_pool, v_pool))
     return attn_mma_launch(q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, n_seg,
                            max_q, H, G, dim, scale, window, keep_first, softcap, out_is_t, out, (cudaStream_t)st);
   if (f32) return dispatch_attn<float>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,
-                                       seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out_is_t, out, (cudaStream_t)st);
+                                       seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out_is_t, out, (cudaStream_t)st);
   return dispatch_attn<__nv_bfloat16>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,
-                                      seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out_is_t, out, (cudaStream_t)st);
+                                      seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out_is_t, out, (cudaStream_t)st);
 }
 
 extern "C" int prl_attn_any(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
@@ -467,4 +481,17 @@ extern "C" int prl_attn_any_masked(const void* q, const void* k_pool, const void
                                    int32_t out_is_t, void* out, prl_stream_t st) {
   return attn_any_impl(q, k_pool, v_pool, f32, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot,
                        n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out_is_t, out, st);
+}
+
+// As prl_attn_any_masked, with two more freedoms: the value rows have their own stride `ldv` >= vdim (values that are a
+// leading slice of wider rows: v_pool may be the key pool itself, so that a latent cache is stored once), and `sink`
+// (NULL = none) holds one fp32 logit per query head that enters the softmax denominator without a key or a value.
+extern "C" int prl_attn_any_sink(const void* q, const void* k_pool, const void* v_pool, int32_t ldv, int32_t f32,
+                                 const int32_t* block_table, int32_t max_blocks, int32_t page_size, const int32_t* seg_start,
+                                 const int32_t* seg_len, const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg,
+                                 int32_t max_q, int32_t H, int32_t G, int32_t dim, int32_t vdim, float scale, int32_t window,
+                                 int32_t keep_first, float softcap, const float* sink, int32_t out_is_t, void* out,
+                                 prl_stream_t st) {
+  return attn_any_impl(q, k_pool, v_pool, f32, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot,
+                       n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, out_is_t, out, st, ldv, sink);
 }

@@ -452,13 +452,13 @@ __global__ void qk_headnorm_cache_kernel(const float* __restrict__ P, int64_t ld
   }
 }
 
-// In-place activation of a column range of the projection buffer: 0 = SiLU
+// In-place activation of a column range of the projection buffer: 0 = SiLU, 1 = tanh
 __global__ void act_cols_kernel(float* __restrict__ P, int64_t ld, int off, int C, int act) {
   pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   float* p = P + (int64_t)blockIdx.x * ld + off + c;
-  *p = silu_f(*p);
+  *p = act == 1 ? tanhf(*p) : silu_f(*p);
 }
 
 // Feed-forward activations of one input: 0 = relu(z)^2
@@ -751,7 +751,7 @@ extern "C" int prl_qk_headnorm_cache(const float* P, int64_t ldp, int32_t off_q,
 }
 
 extern "C" int prl_act_cols(float* P, int64_t ld, int32_t off, int32_t n, int32_t C, int32_t act, prl_stream_t st) {
-  PRL_CHECK_ARG(P && n >= 1 && C >= 1 && off >= 0 && ld >= off + C && act == 0, "prl_act_cols: bad argument");
+  PRL_CHECK_ARG(P && n >= 1 && C >= 1 && off >= 0 && ld >= off + C && (act == 0 || act == 1), "prl_act_cols: bad argument");
   PRL_CUDA(launch_pdl(act_cols_kernel, dim3(n, (C + 255) / 256), dim3(256), (size_t)0, (cudaStream_t)st, P, ld, off, C, act));
   PRL_LAUNCH_CHECK();
   return PRL_OK;

@@ -65,6 +65,15 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
       wsel[(int64_t)c * n + t] = softmax_weights ? expf(best - zsel_max) : sigmoid_f(best);
     }
   }
+  if (softmax_weights == 2) {                    // softmax over ALL experts: the denominator sums every logit
+    float all = 0.f;
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e >= E) break;
+      all += expf(z[e] - zsel_max);
+    }
+    denom = warp_sum(all);
+  }
   if (softmax_weights && lane == 0)
     for (int c = 0; c < top; ++c) wsel[(int64_t)c * n + t] /= denom;
 }
@@ -119,6 +128,15 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const TX* __restrict__ 
       sel[(int64_t)c * n + t] = arg;
       wsel[(int64_t)c * n + t] = softmax_weights ? expf(best - zsel_max) : sigmoid_f(best);
     }
+  }
+  if (softmax_weights == 2) {                    // softmax over ALL experts: the denominator sums every logit
+    float all = 0.f;
+    for (int j = 0; j < kMaxPerLane; ++j) {
+      const int e = lane + 32 * j;
+      if (e >= E) break;
+      all += expf(z[e] - zsel_max);
+    }
+    denom = warp_sum(all);
   }
   if (softmax_weights && lane == 0)
     for (int c = 0; c < top; ++c) wsel[(int64_t)c * n + t] /= denom;
@@ -352,6 +370,20 @@ __global__ void moe_glu_kernel(const float* __restrict__ gu, int64_t ld, int F, 
   out[s * F + c] = T(g * sigmoid_f(beta * g) * (u + 1.f));
 }
 
+// act[s] = act(gate) * up * (w * wscale), act = SiLU: the pair's weight multiplies the expert's OUTPUT; the second
+// projection is linear and has no bias, so the weight is applied to its input instead (in fp32, before the rounding)
+template <typename T>
+__global__ void moe_glu_out_kernel(const float* __restrict__ gu, int64_t ld, int F, const int32_t* __restrict__ perm,
+                                   const float* __restrict__ wsel, float wscale, T* __restrict__ out) {
+  pdl_wait();
+  const int64_t s = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= F) return;
+  const float w = wsel[perm[s]] * wscale;
+  const float g = gu[s * ld + c];
+  out[s * F + c] = T(g * sigmoid_f(g) * gu[s * ld + F + c] * w);
+}
+
 }  // namespace
 }  // namespace prl
 
@@ -439,6 +471,17 @@ extern "C" int prl_moe_glu(const float* gate_up, int64_t ld, int64_t pairs, int3
   dim3 grid((unsigned)pairs, (F + 255) / 256);
   if (f32) PRL_CUDA(launch_pdl(moe_glu_kernel<float>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, limit, beta, (float*)out));
   else PRL_CUDA(launch_pdl(moe_glu_kernel<bf16>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, limit, beta, (bf16*)out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+// Gated expert activation with the pair's weight on the expert's OUTPUT: out = silu(gate) * up * (wsel * wscale).
+extern "C" int prl_moe_glu_out(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm,
+                               const float* wsel, float wscale, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(gate_up && perm && wsel && out && pairs >= 1 && F >= 1 && ld >= 2 * (int64_t)F, "prl_moe_glu_out: bad argument");
+  dim3 grid((unsigned)pairs, (F + 255) / 256);
+  if (f32) PRL_CUDA(launch_pdl(moe_glu_out_kernel<float>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, wscale, (float*)out));
+  else PRL_CUDA(launch_pdl(moe_glu_out_kernel<bf16>, grid, dim3(256), (size_t)0, (cudaStream_t)st, gate_up, ld, F, perm, wsel, wscale, (bf16*)out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

@@ -11,7 +11,12 @@ another design built from the same mixers needs a parser, not new kernels.  Bele
 a sliding window that keeps the first tokens) beside lightning attention (one fixed decay per head), every sublayer
 normed on its input AND its output with gains kept as offsets from one, squared-ReLU and routed (mixture-of-experts)
 feed-forwards, a block of layers that runs several times on the same weights with a cache and state per pass, and
-sinusoidal positions added to the embedding.
+sinusoidal positions added to the embedding.  "Pametar" (`.from_pametar`) adds: latent attention (keys and values of all
+heads expanded from one cached low-rank latent, a rotated key part shared by the heads, a per-head sink logit in the
+softmax denominator), a delta-rule matrix memory with per-channel decay and removal rate, a residual kept as several
+parallel streams that every sublayer reads and writes through learned weights, a statistics-free tanh norm, per-channel
+layer scale and a sigmoid gate on every sublayer's result, routed experts weighted by a softmax over all experts, and a
+hashed token-pair table added to the embedding (the previous token is per-sequence state).
 
 Numerics: the residual stream, every norm, softmax, router-like gate, decay, step size and recurrent state are fp32.
 GEMM operands and the KV cache are bf16, or fp32 when the arena is fp32 (the true-fp32 mode: CUDA-core GEMMs with fp32
@@ -69,6 +74,32 @@ class MlstmSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttnSpec:
+    """Softmax attention over ONE cached latent per token: c = rmsnorm(W_dkv h)[:kv_rank], keys W_uk c and values W_uv c
+    per head, plus `rot_dim` rotated key channels shared by all heads; queries through a normed latent of size q_rank."""
+    heads: int
+    dim: int            # unrotated query / key channels per head
+    rot_dim: int        # rotated channels per head ("rotate half" pairs i, i + rot_dim / 2)
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    rot_base: float
+    scale: float
+    sink: bool = True   # a learned logit per head in the softmax denominator (no key, no value)
+
+
+@dataclass(frozen=True)
+class DeltaSpec:
+    """Delta-rule memory S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r, u the unit key, w = exp(-decay_scale
+    sigmoid(.)) from a rank-`rank` bottleneck, a = sigmoid(.); key and value size are both `dim`."""
+    heads: int
+    dim: int
+    rank: int
+    decay_scale: float = math.exp(-0.5)
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class MoeSpec:
     experts: int
     top: int
@@ -76,6 +107,9 @@ class MoeSpec:
     limit: float
     shared_ff: int = 0          # 0: no shared expert
     shared_limit: float = 0.0
+    score: str = "sigmoid"      # "sigmoid" of the chosen logit | "softmax_all": softmax over ALL experts, not renormalised
+    weight_on: str = "input"    # the score scales the expert's "input" (clamped unit) or its "output" (plain SiLU unit)
+    weight_scale: float = 1.0   # constant factor on the scores
 
 
 @dataclass(frozen=True)
@@ -121,6 +155,7 @@ class MlpSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     kind: str                       # "gla" | "parallel" (attention || state space) | "parallel_lin" (attention || lightning) | "mlstm"
+                                    # | "latent" (latent attention) | "delta" (delta-rule memory): the multi-stream program
     weights_of: int                 # index of the layer whose tensors this layer uses (its own index if it has its own)
     gla: GlaSpec | None = None
     attn: AttnSpec | None = None
@@ -132,6 +167,11 @@ class LayerSpec:
     mlstm: MlstmSpec | None = None
     sandwich: bool = False          # norms before AND after each sublayer (norm1, norm1b, norm2, norm2b) instead of after only
     opens_pass: int | None = None   # this run opens pass t of a repeated block: x <- W_loop [x; x0] + step[t] comes first
+    latent: LatentAttnSpec | None = None
+    delta: DeltaSpec | None = None
+    layer_scale: bool = False       # sublayer results times a per-channel vector (ls1 / ls2)
+    gated: bool = False             # sublayer results times sigmoid(W_rg h + b) of the sublayer's own input
+    hyper: bool = False             # learned read / write / mixing weights over the residual streams (hc1.* / hc2.*)
 
 
 @dataclass(frozen=True)
@@ -145,6 +185,9 @@ class HybridConfig:
     logit_scale: float = 1.0
     norm_offset: float = 0.0        # gains of the width norms are stored as offsets from this value
     loop_times: int = 0             # passes of the repeated block (rows of `loop.step`); 0: no such block
+    norm_kind: str = "rms"          # "tanh": tanh(alpha x) * gain + shift, no statistics (tensors <name>, .b, .alpha)
+    streams: int = 1                # parallel copies of the residual ("tanh" program only)
+    pair_embed: tuple | None = None  # (buckets, mul_prev, mul_cur): hashed (previous, current) token table `bigram`
 
     @property
     def head_rows(self) -> int:
@@ -261,8 +304,81 @@ class HybridConfig:
         cfg.validate()
         return cfg
 
+    # ---- the "Pametar" reading of config.json ---------------------------------------------------------------------
+    @staticmethod
+    def from_pametar(d: dict, tensor_shapes: dict | None = None) -> "HybridConfig":
+        """config.json of a Pametar checkpoint.  `loop` = {start, stop, times} repeats a block of layers on the same
+        tensors (every pass is a run with its own cache and state; nothing happens between passes).  Which of layer
+        scale, gate and stream weights a layer has is read off the tensor names when a file is at hand (all of them
+        otherwise); the rank of the decay bottleneck is the row count of `mix.w1`."""
+        shapes = tensor_shapes or {}
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            m, f, mlp = L["mixer"], L.get("mlp"), None
+            if f is not None:
+                if f.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f.get('kind')!r}")
+                r = f["router"]
+                moe = MoeSpec(int(r["experts"]), int(r["top"]), int(f["expert"]["ff"]), 0.0, score="softmax_all",
+                              weight_on="output", weight_scale=float(r.get("scale", 1.0)))
+                mlp = MlpSpec(ff=0, limit=0.0, kind="moe", moe=moe)
+            has = (lambda name: f"l{i}.{name}" in shapes) if shapes else (lambda name: True)
+            flags = dict(layer_scale=has("ls1"), gated=has("rg1"), hyper=has("hc1.in"))
+            if L["type"] == "latent_attention":
+                rot = m.get("rot") or {}
+                if int(rot.get("dims", m["rot_dim"])) != int(m["rot_dim"]):
+                    raise ValueError(f"layer {i}: the rotated part has {m['rot_dim']} channels but rot.dims = {rot.get('dims')}")
+                spec = LatentAttnSpec(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]),
+                                      int(m["q_rank"]), float(rot.get("base", 10000.0)), float(m["scale"]),
+                                      sink=has("mix.sink"))
+                specs.append(dict(kind="latent", mlp=mlp, latent=spec, **flags))
+            elif L["type"] == "general_delta":
+                rank = m.get("rank")
+                if f"l{i}.mix.w1" in shapes:
+                    rank = shapes[f"l{i}.mix.w1"][0]
+                if rank is None:
+                    raise ValueError(f"layer {i}: the decay rank is neither in the config nor in a tensor shape")
+                specs.append(dict(kind="delta", mlp=mlp, delta=DeltaSpec(int(m["heads"]), int(m["dim"]), int(rank)), **flags))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {L['type']!r}")
+        n, loop = len(specs), d.get("loop")
+        runs = list(range(n))
+        if loop:
+            a, b, times = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+            if not (0 <= a <= b <= n and times >= 1):
+                raise ValueError(f"bad loop {loop}")
+            runs = list(range(a)) + list(range(a, b)) * times + list(range(b, n))
+        layers = tuple(LayerSpec(weights_of=i, **specs[i]) for i in runs)
+        e = d["embedding"]
+        pair = e.get("bigram")
+        if shapes and "bigram" not in shapes:
+            pair = None
+        cfg = HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), float(e.get("scale", 1.0)), layers,
+                           norm_kind="tanh", streams=int(d.get("streams", 1)),
+                           pair_embed=(int(pair["buckets"]), int(pair["mul_prev"]), int(pair["mul_cur"])) if pair else None)
+        cfg.validate()
+        return cfg
+
     def validate(self) -> None:
+        if self.norm_kind == "tanh":
+            if not 1 <= self.streams <= 8 or any(L.kind not in ("latent", "delta") for L in self.layers):
+                raise ValueError("the multi-stream program runs latent-attention and delta-rule layers over 1 to 8 streams")
+            if self.pair_embed is not None and self.pair_embed[0] < 1:
+                raise ValueError(f"bad token-pair table {self.pair_embed}")
+        elif any(L.kind in ("latent", "delta") for L in self.layers):
+            raise ValueError("latent-attention and delta-rule layers belong to the multi-stream program (norm_kind 'tanh')")
         for i, L in enumerate(self.layers):
+            if L.kind == "latent":
+                a = L.latent
+                if a.rot_dim % 2 or a.kv_rank > 256 or a.kv_rank + a.rot_dim > 512 or min(a.heads, a.dim, a.vdim, a.q_rank) < 1:
+                    raise ValueError(f"layer run {i}: bad latent-attention geometry {a} (kv_rank <= 256, even rot_dim)")
+                if not L.hyper and self.streams != 1:
+                    raise ValueError(f"layer run {i}: several streams need the layer's stream weights")
+            elif L.kind == "delta":
+                if L.delta.dim > 256 or L.delta.rank < 1:
+                    raise ValueError(f"layer run {i}: bad delta-rule geometry {L.delta}")
+                if not L.hyper and self.streams != 1:
+                    raise ValueError(f"layer run {i}: several streams need the layer's stream weights")
             if L.kind == "mlstm":
                 if L.mlstm.dim > 256 or L.mlstm.gate_cap < 0:
                     raise ValueError(f"layer run {i}: bad matrix-memory geometry {L.mlstm}")
@@ -274,7 +390,7 @@ class HybridConfig:
                     raise ValueError(f"layer run {i}: bad lightning-attention geometry {r}")
             if L.mlp is not None and L.mlp.kind == "moe" and not 1 <= L.mlp.moe.top <= L.mlp.moe.experts <= 1024:
                 raise ValueError(f"layer run {i}: bad router {L.mlp.moe}")
-            if L.kind in ("mlstm", "parallel_lin"):
+            if L.kind in ("mlstm", "parallel_lin", "latent", "delta"):
                 continue
             if L.kind == "parallel":
                 a, s = L.attn, L.ssd
@@ -300,6 +416,9 @@ class HybridConfig:
         W, out = self.width, []
         for i, L in self._own():
             p = f"l{i}."
+            if L.kind in ("latent", "delta"):
+                out += [(name, shape) for name, shape, _ in self._stream_layer_tensors(i, L)]
+                continue
             if L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
@@ -347,6 +466,52 @@ class HybridConfig:
         if self.loop_times:
             out += [("loop.in", (W, 2 * W)), ("loop.step", (self.loop_times, W))]
         out += [("embed", (self.vocab_size, W)), ("final.norm", (W,)), ("head", (self.vocab_size, W))]
+        if self.norm_kind == "tanh":
+            out += [("final.norm.b", (W,)), ("final.norm.alpha", (1,))]
+        if self.pair_embed is not None:
+            out.append(("bigram", (self.pair_embed[0] + 1, W)))
+        return out
+
+    def _stream_layer_tensors(self, i: int, L: LayerSpec) -> list:
+        """(fused tensor, shape, [(checkpoint tensor, rows)] in row order) of a latent-attention or delta-rule layer.
+        The sublayer gate's projection rides in the mixer's input projection (one GEMM over the same input)."""
+        W, S, p, out = self.width, self.streams, f"l{i}.", []
+        one = lambda name, shape: out.append((p + name, shape, [(p + name, shape[0])]))
+        gate = [(p + "rg1", W)] if L.gated else []
+        if L.kind == "latent":
+            a = L.latent
+            parts = [(p + "mix.dq", a.q_rank), (p + "mix.dkv", a.kv_rank + a.rot_dim)] + gate
+            out.append((p + "mix.in", (sum(n for _, n in parts), W), parts))
+            one("mix.dq.norm", (a.q_rank,)); one("mix.dkv.norm", (a.kv_rank,))
+            one("mix.uq", (a.heads * (a.dim + a.rot_dim), a.q_rank)); one("mix.uk", (a.heads * a.dim, a.kv_rank))
+            one("mix.uv", (a.heads * a.vdim, a.kv_rank))
+            if a.sink:
+                one("mix.sink", (a.heads,))
+            one("mix.o", (W, a.heads * a.vdim))
+        else:
+            c = L.delta
+            nq = c.heads * c.dim
+            parts = [(p + "mix.r", nq), (p + "mix.k", nq), (p + "mix.v", nq), (p + "mix.g", nq), (p + "mix.a", nq),
+                     (p + "mix.w1", c.rank)] + gate
+            out.append((p + "mix.in", (sum(n for _, n in parts), W), parts))
+            one("mix.a.b", (nq,)); one("mix.w2", (nq, c.rank)); one("mix.w0", (nq,)); one("mix.norm", (nq,))
+            one("mix.o", (W, nq))
+        for q in ("1", "2") if L.mlp is not None else ("1",):
+            one("norm" + q, (W,)); one(f"norm{q}.b", (W,)); one(f"norm{q}.alpha", (1,))
+            if L.layer_scale:
+                one("ls" + q, (W,))
+            if L.gated:
+                one(f"rg{q}.b", (W,))
+            if L.hyper:
+                one(f"hc{q}.in", (S,)); one(f"hc{q}.out", (S,)); one(f"hc{q}.mix", (S, S))
+        if L.mlp is not None:
+            e = L.mlp.moe
+            one("mlp.router", (e.experts, W))
+            out.append((p + "mlp.experts.gate_up", (e.experts * 2 * e.ff, W),
+                        [(f"{p}mlp.e{k}.{part}", e.ff) for k in range(e.experts) for part in ("gate", "up")]))
+            out.append((p + "mlp.experts.down", (e.experts * W, e.ff), [(f"{p}mlp.e{k}.down", W) for k in range(e.experts)]))
+            if L.gated:
+                one("rg2", (W, W))
         return out
 
     def checkpoint_slices(self) -> dict[str, tuple[str, int, int]]:
@@ -360,6 +525,10 @@ class HybridConfig:
                 at += n
         for i, L in self._own():
             p = f"l{i}."
+            if L.kind in ("latent", "delta"):
+                for fused, _, parts in self._stream_layer_tensors(i, L):
+                    rows(fused, parts)
+                continue
             if L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
@@ -425,12 +594,24 @@ class HybridConfig:
         m["embed"] = ("embed", 0, self.vocab_size)
         m["final.norm"] = ("final.norm", 0, self.width)
         m["head"] = ("head", 0, self.vocab_size)
+        if self.norm_kind == "tanh":
+            m["final.norm.b"] = ("final.norm.b", 0, self.width)
+            m["final.norm.alpha"] = ("final.norm.alpha", 0, 1)
+        if self.pair_embed is not None:
+            m["bigram"] = ("bigram", 0, self.pair_embed[0] + 1)
         return m
 
     def init_param(self, name: str, view: torch.Tensor, gen: torch.Generator) -> None:
         """Random initialisation for benches and tests: unit gains, small biases, weights of std 1/sqrt(fan_in)."""
         leaf = name.split(".")[-1]
-        if leaf in ("norm1", "norm2", "norm1b", "norm2b") or name == "final.norm":
+        if ".hc1." in name or ".hc2." in name:        # read every stream equally, write to all, keep each stream
+            view.copy_(torch.eye(self.streams) if leaf == "mix" else
+                       torch.full(view.shape, 1.0 / self.streams if leaf == "in" else 1.0))
+        elif leaf == "alpha":
+            view.fill_(0.5)
+        elif leaf in ("ls1", "ls2"):
+            view.fill_(1.0)
+        elif leaf in ("norm1", "norm2", "norm1b", "norm2b") or name == "final.norm":
             view.fill_(1.0 - self.norm_offset)
         elif leaf in ("norm", "out"):
             view.fill_(1.0)
@@ -488,6 +669,18 @@ class _Rows:
                 wide_p = max(wide_p, nq + a.kv_heads * a.dim + 2 * r.heads * (r.dim + r.vdim))
                 wide_o, wide_q = max(wide_o, a.heads * a.vdim), max(wide_q, nq)
                 wide_o2 = max(wide_o2, r.heads * r.vdim)
+            elif L.kind == "latent":
+                a = L.latent               # buffer roles: see HybridEngine._latent_mixer
+                wide_p = max(wide_p, a.q_rank + a.kv_rank + a.rot_dim + (W if L.gated else 0))
+                wide_aux = max(wide_aux, a.heads * (a.dim + a.rot_dim))
+                wide_o = max(wide_o, a.heads * a.kv_rank, a.heads * a.vdim, a.q_rank)
+                wide_o2 = max(wide_o2, a.heads * a.dim, a.heads * a.vdim)
+                wide_q = max(wide_q, a.heads * (a.kv_rank + a.rot_dim))
+            elif L.kind == "delta":
+                c = L.delta
+                nq = c.heads * c.dim
+                wide_p = max(wide_p, 5 * nq + c.rank + (W if L.gated else 0))
+                wide_aux, wide_o = max(wide_aux, nq), max(wide_o, nq)
             else:
                 a, s = L.attn, L.ssd
                 nq = a.heads * a.dim
@@ -504,6 +697,8 @@ class _Rows:
         i32 = dict(dtype=torch.int32, device=d)
         self.n = n
         self.x = torch.zeros(n * W, **f32)                      # the residual stream
+        if cfg.norm_kind == "tanh":                             # ... or its parallel streams [row][stream][W]
+            self.xs = torch.zeros(n * cfg.streams * W, **f32)
         self.xa = torch.zeros(n * W, dtype=T, device=d)         # its copy in the GEMM operand type
         self.P = torch.zeros(n * wide_p, **f32)                 # projection output of the current sublayer
         self.aux = torch.zeros(n * wide_aux, **f32)             # decay logits (GLA) / convolved x, B, C (state-space)
@@ -582,8 +777,20 @@ class HybridEngine(EngineCore):
         self.k_pool, self.v_pool, self.conv_state, self.ssd_state, self.gla_state, self.rot_freq = {}, {}, {}, {}, {}, {}
         self.tc_attn: dict[int, bool] = {}
         self.lin_state, self.lin_decay, self.mlstm_state, self.mlstm_m = {}, {}, {}, {}
+        self.lat_pool, self.delta_state = {}, {}
+        if cfg.pair_embed is not None:                   # the last token of the sequence's previous portion
+            self.prev_token = self.states.add("prev_token", (1,), dtype=torch.int32)
         for i, L in enumerate(cfg.layers):               # one cache / state per layer RUN, also where weights are shared
-            if L.kind == "gla":
+            if L.kind == "latent":
+                a = L.latent                             # one row per token: [latent | rotated shared key part]
+                self.lat_pool[i] = torch.zeros(self.n_pages, PAGE_SIZE, a.kv_rank + a.rot_dim, dtype=self.op_dtype, device=d)
+                f = [a.rot_base ** (-2.0 * k / a.rot_dim) for k in range(a.rot_dim // 2)] or [0.0]
+                self.rot_freq[i] = torch.tensor(f, dtype=torch.float64, device=d)
+            elif L.kind == "delta":
+                c = L.delta
+                n = int(lib.prl_delta_state_floats(c.heads, c.dim, c.dim))
+                self.delta_state[i] = self.states.add(f"l{i}.delta", (n,))
+            elif L.kind == "gla":
                 g = L.gla
                 n = int(lib.prl_lin_scan_state_floats(g.heads, g.dim, g.vdim))
                 self.gla_state[i] = self.states.add(f"l{i}.gla", (n,))
@@ -625,8 +832,16 @@ class HybridEngine(EngineCore):
         # fp32 copies of the small parameter vectors (gains, biases, taps, per-head constants): exact for bf16 weights
         self.vec: dict[str, torch.Tensor] = {}
         for name, shape in cfg.fused_shapes():
-            if len(shape) == 1 or name.endswith("mix.right.conv") or name == "loop.step":
+            if len(shape) == 1 or name.endswith("mix.right.conv") or name == "loop.step" or name.endswith(".mix") and ".hc" in name:
                 self.vec[name] = torch.zeros(shape, dtype=torch.float32, device=d)
+        # per-head transposes W_uk,h^T [kv_rank, dim] of the latent layers' key expansion (operand type): the B operand
+        # of the product that absorbs the expansion into the query.  Refreshed with the small vectors on a weight flip.
+        self.uk_t = {L.weights_of: torch.zeros(L.latent.heads, L.latent.kv_rank, L.latent.dim, dtype=self.op_dtype, device=d)
+                     for L in cfg.layers if L.kind == "latent"}
+        if cfg.norm_kind == "tanh":                      # stream weights of layers without their own: the plain residual sum
+            S = cfg.streams
+            self.stream_ones = torch.ones(S, dtype=torch.float32, device=d)
+            self.stream_eye = torch.eye(S, dtype=torch.float32, device=d)
         if cfg.positions == "sinusoid":
             W = cfg.width
             self.pos_freq = torch.tensor([10000.0 ** (-2.0 * k / W) for k in range((W + 1) // 2)], dtype=torch.float64, device=d)
@@ -653,6 +868,9 @@ class HybridEngine(EngineCore):
                     t.add_(cfg.norm_offset)              # gains stored as offsets
         if cfg.logit_scale != 1.0:
             self.vec["final.norm"].mul_(cfg.logit_scale)   # logits = head(norm(x)) * scale: folded into the last gain
+        for j, t in self.uk_t.items():
+            H, r, dm = t.shape
+            t.copy_(self.arena.view(f"l{j}.mix.uk").view(H, dm, r).transpose(1, 2))
 
     @staticmethod
     def scan_geometry(L) -> list:
@@ -663,11 +881,14 @@ class HybridEngine(EngineCore):
             return [(L.mlstm.heads, L.mlstm.dim, L.mlstm.vdim + 1)]
         if L.kind == "parallel_lin":
             return [(L.lin.heads, L.lin.dim, L.lin.vdim)]
+        if L.kind in ("latent", "delta"):
+            return []                      # the delta rule has a scan of its own (prl_delta_scan), walked token by token
         return [(L.ssd.heads, L.ssd.state, L.ssd.vdim)]
 
     def kv_bytes_per_token(self) -> int:
         e = 4 if self.f32 else 2
-        return sum(L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * e for L in self.cfg.layers if L.attn is not None)
+        return (sum(L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * e for L in self.cfg.layers if L.attn is not None)
+                + sum((L.latent.kv_rank + L.latent.rot_dim) * e for L in self.cfg.layers if L.latent is not None))
 
     # ---- GEMM dispatch ------------------------------------------------------------------------------------------------
     def _mm(self, src: torch.Tensor, K: int, w_name: str, N: int, out: torch.Tensor, n: int, split: bool = False) -> int:
@@ -691,6 +912,8 @@ class HybridEngine(EngineCore):
     def _layers(self, R: _Rows, n: int, ns: int, max_q: int, row_pos: torch.Tensor, seg_pos0: torch.Tensor,
                 trace=None, decode: bool = False) -> None:
         cfg, lib, st, f32 = self.cfg, self.lib, self._st, int(self.f32)
+        if cfg.norm_kind == "tanh":
+            return self._stream_layers(R, n, ns, max_q, row_pos, seg_pos0, trace)
         W, eps, vec = cfg.width, cfg.eps, self.vec
         seg_start, seg_len, seg_slot = R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr()
         P, x, xa = R.P.data_ptr(), R.x.data_ptr(), R.xa.data_ptr()
@@ -860,19 +1083,24 @@ class HybridEngine(EngineCore):
         lib, st, W, f32 = self.lib, self._st, self.cfg.width, int(self.f32)
         pairs = n * e.top
         route = (R.sel.data_ptr(), R.wsel.data_ptr(), R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), st)
+        mode = 2 if e.score == "softmax_all" else 0     # weights: sigmoid of the chosen logit | softmax over all experts
         if (W + e.experts) * 4 <= 160 * 1024 and not self.unfused_router:
-            _lib.check(lib.prl_moe_router(R.xa.data_ptr(), f32, self.arena.ptr(w + "mlp.router"), f32, n, W, e.experts, e.top, 0,
+            _lib.check(lib.prl_moe_router(R.xa.data_ptr(), f32, self.arena.ptr(w + "mlp.router"), f32, n, W, e.experts, e.top, mode,
                                           *route))
         else:
             _lib.check(lib.prl_gemm_any(R.xa.data_ptr(), f32, W, self.arena.ptr(w + "mlp.router"), f32, W, n, e.experts, W,
                                         R.router.data_ptr(), e.experts, st))
-            _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, 0, *route))
+            _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, mode, *route))
         tiles = int(lib.prl_moe_max_tiles(pairs, e.experts))
         table = (R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), tiles)
         _lib.check(lib.prl_moe_gemm(R.xa.data_ptr(), f32, W, n, self.arena.ptr(w + "mlp.experts.gate_up"), f32,
                                     2 * e.ff * W, W, *table, 2 * e.ff, W, R.P.data_ptr(), 2 * e.ff, 0, st))
-        _lib.check(lib.prl_moe_glu(R.P.data_ptr(), 2 * e.ff, pairs, e.ff, R.perm.data_ptr(), R.wsel.data_ptr(), e.limit, beta,
-                                   R.moe_act.data_ptr(), f32, st))
+        if e.weight_on == "output":      # plain SiLU unit, the score (times a constant) on the expert's output
+            _lib.check(lib.prl_moe_glu_out(R.P.data_ptr(), 2 * e.ff, pairs, e.ff, R.perm.data_ptr(), R.wsel.data_ptr(),
+                                           e.weight_scale, R.moe_act.data_ptr(), f32, st))
+        else:
+            _lib.check(lib.prl_moe_glu(R.P.data_ptr(), 2 * e.ff, pairs, e.ff, R.perm.data_ptr(), R.wsel.data_ptr(), e.limit, beta,
+                                       R.moe_act.data_ptr(), f32, st))
         _lib.check(lib.prl_moe_gemm(R.moe_act.data_ptr(), f32, e.ff, 0, self.arena.ptr(w + "mlp.experts.down"), f32,
                                     W * e.ff, e.ff, *table, W, e.ff, R.moe_out.data_ptr(), W, 1, st))
         return R.moe_out
@@ -944,9 +1172,146 @@ class HybridEngine(EngineCore):
                     gain1=vec[w + "mix.right.out"], s1=L.right_scale,
                     post_gain=vec[w + "norm1b"] if L.sandwich else vec[w + "norm1"], next_gain=self._next_gain(i, True))
 
-    def _embed(self, R, n, tokens, positions) -> None:
+    # ---- the multi-stream program: latent attention and delta-rule layers ------------------------------------------------
+    def _stream_weights(self, i: int, q: str):
+        """(read weights, write weights, mixing matrix) of sublayer q of run i; a layer without them sums plainly."""
+        L = self.cfg.layers[i]
+        if L.hyper:
+            p = f"l{L.weights_of}.hc{q}."
+            return self.vec[p + "in"], self.vec[p + "out"], self.vec[p + "mix"]
+        return self.stream_ones, self.stream_ones, self.stream_eye
+
+    def _tanh_norm(self, name: str):
+        return self.vec[name + ".alpha"], self.vec[name], self.vec[name + ".b"]
+
+    def _next_reader(self, i: int, after_mixer: bool):
+        """(read weights, alpha, gain, shift) of whatever reads the streams after this sublayer of run i, or None at
+        the end of the stack (the model's last norm gathers the wanted rows itself)."""
+        L = self.cfg.layers[i]
+        if after_mixer and L.mlp is not None:
+            return (self._stream_weights(i, "2")[0], *self._tanh_norm(f"l{L.weights_of}.norm2"))
+        if i + 1 < len(self.cfg.layers):
+            return (self._stream_weights(i + 1, "1")[0], *self._tanh_norm(f"l{self.cfg.layers[i + 1].weights_of}.norm1"))
+        return None
+
+    def _stream_close(self, R, n, i, q, y, k, gate, ldg) -> None:
+        """The sublayer's result (k slices [k][n][W]) back into the streams: layer scale, gate, stream update, and the
+        next reader's normed input into R.xa (prl_streams_close)."""
+        L, W = self.cfg.layers[i], self.cfg.width
+        w = f"l{L.weights_of}."
+        _, w_out, mix = self._stream_weights(i, q)
+        nxt = self._next_reader(i, q == "1")
+        ptr = lambda t: None if t is None else t.data_ptr()
+        nx = [ptr(t) for t in nxt] if nxt is not None else [None] * 4
+        _lib.check(self.lib.prl_streams_close(y.data_ptr(), W, k, n * W, ptr(self.vec.get(w + "ls" + q)) if L.layer_scale else None,
+                                              gate, ldg, ptr(self.vec.get(f"{w}rg{q}.b")) if L.gated else None, mix.data_ptr(),
+                                              w_out.data_ptr(), self.cfg.streams, n, W, R.xs.data_ptr(), *nx, R.xa.data_ptr(),
+                                              int(self.f32), self._st))
+
+    def _stream_layers(self, R, n, ns, max_q, row_pos, seg_pos0, trace=None) -> None:
+        """Layer program of the "tanh" family.  On entry R.xa holds the first mixer's normed input (the embedding kernel
+        wrote it); every closing kernel leaves the next sublayer's.  A sublayer's gate projection rides in its first GEMM
+        (mixer) or is one more GEMM over the same input (feed-forward)."""
+        cfg, W, S = self.cfg, self.cfg.width, self.cfg.streams
+        segs = (R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr(), ns)
+        for i, L in enumerate(cfg.layers):
+            w = f"l{L.weights_of}."
+            if L.kind == "latent":
+                y, k, gate, ldg = self._latent_mixer(R, n, i, L, w, segs, max_q, row_pos, seg_pos0)
+            else:
+                y, k, gate, ldg = self._delta_mixer(R, n, i, L, w, segs)
+            self._stream_close(R, n, i, "1", y, k, gate, ldg)
+            if L.mlp is not None:
+                gate = None
+                if L.gated:
+                    self._mm(R.xa, W, w + "rg2", W, R.y1, n)
+                    gate = R.y1.data_ptr()
+                y = self._routed_ff(R, n, w, L.mlp.moe, L.mlp.beta)
+                self._stream_close(R, n, i, "2", y, L.mlp.moe.top, gate, W)
+            if trace is not None:
+                trace.append(R.xs[:n * S * W].view(n, S, W).sum(1))
+
+    def _latent_mixer(self, R, n, i, L, w, segs, max_q, row_pos, seg_pos0):
+        """Latent attention with the key expansion absorbed into the query and the value expansion applied to the
+        attention output, so that the cache holds one row [latent | rotated shared key part] per token and attention
+        runs as one shared key head of size kv_rank + rot_dim whose values are the row's first kv_rank channels.
+        Buffers: P = [dq | dkv | gate] (fp32); ya = the normed query latent, later the attention output (operand type);
+        aux = W_uq cq (fp32); yb = the heads' unrotated query parts, later the expanded values (operand type); q = the
+        attention query [n][H][kv_rank + rot_dim]; o = the absorbed query channels, later the expanded values (fp32)."""
+        a, lib, st, vec, f32, W = L.latent, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        seg_start, seg_len, seg_slot, ns = segs
+        H, rk, dr = a.heads, a.kv_rank, a.rot_dim
+        kd = rk + dr
+        ld = a.q_rank + kd + (W if L.gated else 0)
+        P = R.P.data_ptr()
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        _lib.check(lib.prl_latent_prep(P, ld, 0, a.q_rank, a.q_rank, rk, dr, self.rot_freq[i].data_ptr(),
+                                       vec[w + "mix.dq.norm"].data_ptr(), vec[w + "mix.dkv.norm"].data_ptr(), self.cfg.eps,
+                                       row_pos.data_ptr(), R.row_slot.data_ptr(), self.block_table.data_ptr(), self.max_blocks,
+                                       PAGE_SIZE, n, R.ya.data_ptr(), self.lat_pool[i].data_ptr(), f32, st))
+        hq = H * (a.dim + dr)
+        self._mm(R.ya, a.q_rank, w + "mix.uq", hq, R.aux, n)
+        _lib.check(lib.prl_latent_query(R.aux.data_ptr(), hq, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(),
+                                        row_pos.data_ptr(), R.yb.data_ptr(), R.q.data_ptr(), f32, st))
+        # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers
+        self._mm_heads(R.yb, H * a.dim, a.dim, self.uk_t[L.weights_of].data_ptr(), a.dim, rk * a.dim, n, rk, a.dim,
+                       R.o, H * rk, rk, H)
+        _lib.check(lib.prl_store_groups(R.o.data_ptr(), H * rk, n, H, rk, R.q.data_ptr(), kd, f32, st))
+        pool = self.lat_pool[i].data_ptr()
+        _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
+                                         PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd, rk,
+                                         a.scale, 0, 0, 0.0, vec[w + "mix.sink"].data_ptr() if a.sink else None, 1,
+                                         R.ya.data_ptr(), st))
+        # v[h] = W_uv,h o_lat[h], then the output projection over the concatenated heads
+        self._mm_heads(R.ya, H * rk, rk, self.arena.ptr(w + "mix.uv"), rk, a.vdim * rk, n, a.vdim, rk,
+                       R.o, H * a.vdim, a.vdim, H)
+        _lib.check(lib.prl_store_groups(R.o.data_ptr(), H * a.vdim, n, 1, H * a.vdim, R.yb.data_ptr(), H * a.vdim, f32, st))
+        k0 = self._mm(R.yb, H * a.vdim, w + "mix.o", W, R.y0, n, split=True)
+        return R.y0, k0, (P + 4 * (a.q_rank + kd)) if L.gated else None, ld
+
+    def _mm_heads(self, src, lda, a_step, w_ptr, ldw, w_step, n, N, K, out, ldc, c_step, heads) -> None:
+        """out[:, h*c_step : +N] (fp32) = src[:, h*a_step : +K] @ W_h[N, K]^T for every head h (W_h = w_ptr + h * w_step)."""
+        f32 = int(self.f32)
+        _lib.check(self.lib.prl_gemm_any_batched(src.data_ptr(), f32, lda, a_step, w_ptr, f32, ldw, w_step, n, N, K,
+                                                 out.data_ptr(), ldc, c_step, heads, self._st))
+
+    def _delta_mixer(self, R, n, i, L, w, segs):
+        """Delta-rule memory: one projection [r | k | v | g | a | w1 | gate]; the decay logits come through the tanh
+        bottleneck in fp32; prl_delta_scan forms the unit key, decay and removal rate itself and walks the tokens."""
+        c, lib, st, vec, f32, W = L.delta, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        seg_start, seg_len, seg_slot, ns = segs
+        nq = c.heads * c.dim
+        ld = 5 * nq + c.rank + (W if L.gated else 0)
+        P = R.P.data_ptr()
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        _lib.check(lib.prl_act_cols(P, ld, 5 * nq, n, c.rank, 1, st))                 # tanh of the bottleneck
+        _lib.check(lib.prl_gemm_any(P + 4 * 5 * nq, 1, ld, self.arena.ptr(w + "mix.w2"), f32, c.rank, n, nq, c.rank,
+                                    R.aux.data_ptr(), nq, st))
+        _lib.check(lib.prl_delta_scan(P, ld, 0, nq, 2 * nq, 4 * nq, R.aux.data_ptr(), nq, vec[w + "mix.w0"].data_ptr(),
+                                      vec[w + "mix.a.b"].data_ptr(), c.decay_scale, c.unit_eps, c.heads, c.dim, c.dim,
+                                      seg_start, seg_len, seg_slot, ns, self.delta_state[i].data_ptr(), R.o.data_ptr(), nq, st))
+        _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, nq, P + 4 * 3 * nq, ld, vec[w + "mix.norm"].data_ptr(), nq, c.dim, n,
+                                     nq, 1, 0, 1, self.cfg.eps, R.ya.data_ptr(), f32, st))
+        k0 = self._mm(R.ya, nq, w + "mix.o", W, R.y0, n, split=True)
+        return R.y0, k0, (P + 4 * (5 * nq + c.rank)) if L.gated else None, ld
+
+    def _embed(self, R, n, tokens, positions, ns=None) -> None:
         cfg, lib, st = self.cfg, self.lib, self._st
-        if cfg.positions == "sinusoid":
+        if cfg.norm_kind == "tanh":
+            # token (+ hashed token pair) embedding into every stream, and the first mixer's normed input
+            pe = cfg.pair_embed
+            w_in = self._stream_weights(0, "1")[0] if cfg.layers else self.stream_ones
+            alpha, gain, shift = self._tanh_norm(f"l{cfg.layers[0].weights_of}.norm1" if cfg.layers else "final.norm")
+            prev = self.prev_token.data_ptr() if pe else None
+            _lib.check(lib.prl_embed_pair(tokens.data_ptr(), positions.data_ptr(), R.row_slot.data_ptr(), R.row_back.data_ptr(),
+                                          prev, self.arena.ptr("embed"), self.arena.ptr("bigram") if pe else None, int(self.f32),
+                                          cfg.embed_scale, *(pe or (0, 0, 0)), n, cfg.width, cfg.vocab_size, cfg.streams,
+                                          w_in.data_ptr(), alpha.data_ptr(), gain.data_ptr(), shift.data_ptr(),
+                                          R.xs.data_ptr(), R.xa.data_ptr(), st))
+            if pe:
+                _lib.check(lib.prl_last_token(tokens.data_ptr(), R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr(),
+                                              n if ns is None else ns, prev, st))
+        elif cfg.positions == "sinusoid":
             x0a = R.x0a.data_ptr() if cfg.loop_times else None
             _lib.check(lib.prl_embed_sinusoid(tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale,
                                               self.pos_freq.data_ptr(), positions.data_ptr(), n, cfg.width, cfg.vocab_size,
@@ -955,6 +1320,18 @@ class HybridEngine(EngineCore):
             _lib.check(lib.prl_embed_scale(tokens.data_ptr(), self.arena.ptr("embed"), int(self.f32), cfg.embed_scale, n,
                                            cfg.width, cfg.vocab_size, R.x.data_ptr(), R.xa.data_ptr(), st))
 
+    def _final_norm(self, R, rows, n_out) -> None:
+        """R.xa[:n_out] = the model's last norm of the rows `rows` (None: the first n_out rows) of the residual."""
+        cfg, lib, st = self.cfg, self.lib, self._st
+        if cfg.norm_kind == "tanh":
+            alpha, gain, shift = self._tanh_norm("final.norm")
+            _lib.check(lib.prl_streams_open(R.xs.data_ptr(), rows, n_out, cfg.streams, cfg.width, self.stream_ones.data_ptr(),
+                                            alpha.data_ptr(), gain.data_ptr(), shift.data_ptr(), R.xa.data_ptr(),
+                                            int(self.f32), st))
+        else:
+            _lib.check(lib.prl_rmsnorm_rows(R.x.data_ptr(), rows, self.vec["final.norm"].data_ptr(), cfg.eps, n_out, cfg.width,
+                                            R.xa.data_ptr(), int(self.f32), st))
+
     # ---- one token for every slot (captured into the engine's CUDA graph) ---------------------------------------------
     def _step_kernels(self) -> None:
         cfg, lib, R, B = self.cfg, self.lib, self._dec, self.B
@@ -962,8 +1339,7 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_decode_rows(self.active.data_ptr(), B, R.seg[1].data_ptr(), R.row_slot.data_ptr(), st))
         self._embed(R, B, self.tokens, self.positions)
         self._layers(R, B, B, 1, self.positions, self.positions, decode=True)
-        _lib.check(lib.prl_rmsnorm_rows(R.x.data_ptr(), None, self.vec["final.norm"].data_ptr(), cfg.eps, B, cfg.width,
-                                        R.xa.data_ptr(), int(self.f32), st))
+        self._final_norm(R, None, B)
         self._mm(R.xa, cfg.width, "head", cfg.vocab_size, self.logits, B)
 
     # ---- a packed batch of prompt portions (prefill chunks, token streams) --------------------------------------------
@@ -1005,15 +1381,14 @@ class HybridEngine(EngineCore):
         R.row_back[:n].copy_(torch.tensor(back, dtype=i32), non_blocking=True)
         R.seg[:, :ns].copy_(torch.tensor(meta, dtype=i32), non_blocking=True)
         self._st = st = _lib.stream_ptr()
-        self._embed(R, n, R.tokens, R.row_pos)
+        self._embed(R, n, R.tokens, R.row_pos, ns)
         self._layers(R, n, ns, max(k for _, _, k in segs), R.row_pos, R.seg[2], trace=trace)
         self.stats["prefill_tokens"] += n
         if not want_rows:
             return None
         nw = len(want_rows)
         R.want[:nw].copy_(torch.tensor(want_rows, dtype=i32), non_blocking=True)
-        _lib.check(lib.prl_rmsnorm_rows(R.x.data_ptr(), R.want.data_ptr(), self.vec["final.norm"].data_ptr(), cfg.eps, nw,
-                                        cfg.width, R.xa.data_ptr(), int(self.f32), st))
+        self._final_norm(R, R.want.data_ptr(), nw)
         out = torch.empty(nw, cfg.vocab_size, dtype=torch.float32, device=self.dev)
         self._mm(R.xa, cfg.width, "head", cfg.vocab_size, out, nw)
         return out

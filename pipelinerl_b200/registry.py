@@ -108,6 +108,11 @@ def _belelorn_config(config: dict, shapes: dict):
     return HybridConfig.from_belelorn(config, shapes)
 
 
+def _pametar_config(config: dict, shapes: dict):
+    from .hybrid import HybridConfig
+    return HybridConfig.from_pametar(config, shapes)
+
+
 def _hybrid_engine():
     from .hybrid import HybridEngine
     return HybridEngine
@@ -116,6 +121,7 @@ def _hybrid_engine():
 register(Family("Qwen2ForCausalLM", _qwen2_config, _qwen2_engine, (torch.bfloat16,)))
 register(Family("Povurax", _povurax_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 register(Family("Belelorn", _belelorn_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
+register(Family("Pametar", _pametar_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 
 
 def parse_dtype(name: str) -> torch.dtype:
