@@ -86,11 +86,12 @@ def latent_attention(h, wt, p, m, eps, round_in=None):
     out = torch.zeros(T, H, dv, dtype=F64)
     for head in range(H):
         q_rot = rotate_half(q[:, head, d:], base)
+        sink = float(wt[p + "sink"][head]) if p + "sink" in wt else -math.inf       # a checkpoint without sinks: plain softmax
         for t in range(T):
             s = (k[:t + 1, head] @ q[t, head, :d] + k_rot[:t + 1] @ q_rot[t]) * m["scale"]
-            top = max(float(s.max()), float(wt[p + "sink"][head]))
+            top = max(float(s.max()), sink)
             e = torch.exp(s - top)
-            den = e.sum() + math.exp(float(wt[p + "sink"][head]) - top)
+            den = e.sum() + math.exp(sink - top)
             out[t, head] = (e / den) @ v[:t + 1, head]
     return _mm(out.reshape(T, H * dv), wt[p + "o"], round_in)
 
@@ -119,15 +120,20 @@ def general_delta(h, wt, p, m, eps, round_in=None):
 
 
 # ---- feed-forward -----------------------------------------------------------------------------------------------------
-def routed_experts(h, wt, p, f, round_in=None):
+def routed_experts(h, wt, p, f, round_in=None, margins=None):
     """Softmax over all experts; the `top` largest are taken; each taken expert's output is weighted by its softmax
-    score times a constant (scores are not renormalised over the taken ones)."""
+    score times a constant (scores are not renormalised over the taken ones).  `margins`, a list, receives per token the
+    gap between the last taken and the first left-out router logit (inf when all are taken)."""
     T, W = h.shape
     E, top, scale = f["router"]["experts"], f["router"]["top"], f["router"].get("scale", 1.0)
-    s = torch.softmax(_mm(h, wt[p + "router"], round_in), dim=-1)
+    z = _mm(h, wt[p + "router"], round_in)
+    s = torch.softmax(z, dim=-1)
     out = torch.zeros(T, W, dtype=F64)
     for t in range(T):
-        order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
+        ranked = sorted(range(E), key=lambda e: (-float(s[t, e]), e))
+        order = ranked[:top]
+        if margins is not None:
+            margins.append(float(z[t, ranked[top - 1]] - z[t, ranked[top]]) if top < E else math.inf)
         for e in order:
             q = f"{p}e{e}."
             a = silu(_mm(h[t:t + 1], wt[q + "gate"], round_in)) * _mm(h[t:t + 1], wt[q + "up"], round_in)
@@ -172,8 +178,9 @@ def layer_runs(cfg):
     return list(range(a)) + list(range(a, b)) * k + list(range(b, n))
 
 
-def forward(tokens, wt, cfg, round_in=None, trace=None):
-    """Logits [T, vocab] of one sequence.  `trace`, a list, receives the sum of the streams after every layer run."""
+def forward(tokens, wt, cfg, round_in=None, trace=None, margins=None):
+    """Logits [T, vocab] of one sequence.  `trace`, a list, receives the sum of the streams after every layer run;
+    `margins`, a list, one list of router gaps (see routed_experts) per routed feed-forward that runs."""
     eps = cfg["norm"]["eps"]
     x = embed(tokens, wt, cfg)
     S = int(cfg.get("streams", 1))
@@ -183,7 +190,78 @@ def forward(tokens, wt, cfg, round_in=None, trace=None):
         mixer = {"latent_attention": latent_attention, "general_delta": general_delta}[L["type"]]
         xs = sublayer(xs, lambda h: mixer(h, wt, name + ".mix.", L["mixer"], eps, round_in), wt, name, 1, round_in)
         if L.get("mlp") is not None:
-            xs = sublayer(xs, lambda h: routed_experts(h, wt, name + ".mlp.", L["mlp"], round_in), wt, name, 2, round_in)
+            gaps = [] if margins is not None else None
+            xs = sublayer(xs, lambda h: routed_experts(h, wt, name + ".mlp.", L["mlp"], round_in, gaps), wt, name, 2, round_in)
+            if margins is not None:
+                margins.append(gaps)
         if trace is not None:
             trace.append(xs.sum(0))
     return _mm(tanh_norm(xs.sum(0), wt, "final.norm"), wt["head"], round_in)
+
+
+# ---- random checkpoints for the tests -----------------------------------------------------------------------------------
+def tensor_shapes(cfg, layer_scale=True, gated=True, hyper=True, sink=True):
+    """Checkpoint tensor names and shapes of a configuration; the four flags leave out optional parts of every layer."""
+    W, S, out = cfg["width"], int(cfg.get("streams", 1)), {}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        if L["type"] == "latent_attention":
+            H, d, dr, dv, rk, rq = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out.update({p + "mix.dq": (rq, W), p + "mix.dq.norm": (rq,), p + "mix.uq": (H * (d + dr), rq),
+                        p + "mix.dkv": (rk + dr, W), p + "mix.dkv.norm": (rk,), p + "mix.uk": (H * d, rk),
+                        p + "mix.uv": (H * dv, rk), p + "mix.o": (W, H * dv)})
+            if sink:
+                out[p + "mix.sink"] = (H,)
+        else:
+            n, r = m["heads"] * m["dim"], m["rank"]
+            for name in ("r", "k", "v", "g", "a"):
+                out[p + "mix." + name] = (n, W)
+            out.update({p + "mix.a.b": (n,), p + "mix.w1": (r, W), p + "mix.w2": (n, r), p + "mix.w0": (n,),
+                        p + "mix.norm": (n,), p + "mix.o": (W, n)})
+        for q in ("1", "2") if L.get("mlp") is not None else ("1",):
+            out.update({f"{p}norm{q}": (W,), f"{p}norm{q}.b": (W,), f"{p}norm{q}.alpha": ()})
+            if layer_scale:
+                out[f"{p}ls{q}"] = (W,)
+            if gated:
+                out.update({f"{p}rg{q}": (W, W), f"{p}rg{q}.b": (W,)})
+            if hyper:
+                out.update({f"{p}hc{q}.in": (S,), f"{p}hc{q}.out": (S,), f"{p}hc{q}.mix": (S, S)})
+        f = L.get("mlp")
+        if f is not None:
+            out[p + "mlp.router"] = (f["router"]["experts"], W)
+            for e in range(f["router"]["experts"]):
+                out.update({f"{p}mlp.e{e}.gate": (f["expert"]["ff"], W), f"{p}mlp.e{e}.up": (f["expert"]["ff"], W),
+                            f"{p}mlp.e{e}.down": (W, f["expert"]["ff"])})
+    out.update({"embed": (cfg["vocab"], W), "final.norm": (W,), "final.norm.b": (W,), "final.norm.alpha": (),
+                "head": (cfg["vocab"], W)})
+    if cfg["embedding"].get("bigram") is not None:
+        out["bigram"] = (cfg["embedding"]["bigram"]["buckets"] + 1, W)
+    return out
+
+
+def random_weights(cfg, seed=0, dtype=torch.bfloat16, **parts):
+    """Random tensors, rounded to `dtype` so that the engine and the oracle see the same numbers.  Matrices have unit
+    row gain (std 1/sqrt(fan_in)); gains, stream weights and scales are spread around their neutral values."""
+    g = torch.Generator().manual_seed(seed)
+    S, wt = int(cfg.get("streams", 1)), {}
+    for name, shape in tensor_shapes(cfg, **parts).items():
+        leaf = name.split(".")[-1]
+        rnd = lambda std=1.0: torch.randn(shape, generator=g) * std
+        if ".hc" in name:
+            t = {"in": 1.0 / S + rnd(0.2), "out": 1.0 + rnd(0.2), "mix": torch.eye(S) + rnd(0.15)}[leaf]
+        elif leaf == "alpha":
+            t = 0.4 + 0.2 * torch.rand(shape, generator=g)
+        elif leaf in ("norm1", "norm2", "norm", "ls1", "ls2") or name == "final.norm":
+            t = 1.0 + rnd(0.2)
+        elif name in ("embed", "bigram"):
+            t = rnd(0.7)
+        elif leaf == "b":
+            t = rnd(0.3)
+        elif leaf in ("sink", "w0"):
+            t = rnd(1.0)
+        elif leaf == "router":
+            t = rnd(4.0 / math.sqrt(shape[-1]))                             # well separated scores
+        else:
+            t = rnd(1.0 / math.sqrt(shape[-1]))
+        wt[name] = t.to(dtype).to(F64)
+    return wt
