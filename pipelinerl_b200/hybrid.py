@@ -1258,10 +1258,16 @@ class HybridEngine(EngineCore):
                        R.o, H * rk, rk, H)
         _lib.check(lib.prl_store_groups(R.o.data_ptr(), H * rk, n, H, rk, R.q.data_ptr(), kd, f32, st))
         pool = self.lat_pool[i].data_ptr()
-        _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
-                                         PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd, rk,
-                                         a.scale, 0, 0, 0.0, vec[w + "mix.sink"].data_ptr() if a.sink else None, 1,
-                                         R.ya.data_ptr(), st))
+        sink = vec[w + "mix.sink"].data_ptr() if a.sink else None
+        if not self.f32 and not self.force_plain_attn and lib.prl_attn_latent_fits(kd, rk, PAGE_SIZE):
+            # bf16: the heads stacked into the M dimension of tensor-core products over the shared key rows
+            _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE,
+                                           seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, kd, rk, a.scale,
+                                           sink, R.ya.data_ptr(), st))
+        else:
+            _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
+                                             PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
+                                             rk, a.scale, 0, 0, 0.0, sink, 1, R.ya.data_ptr(), st))
         # v[h] = W_uv,h o_lat[h], then the output projection over the concatenated heads
         self._mm_heads(R.ya, H * rk, rk, self.arena.ptr(w + "mix.uv"), rk, a.vdim * rk, n, a.vdim, rk,
                        R.o, H * a.vdim, a.vdim, H)

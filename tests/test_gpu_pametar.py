@@ -289,6 +289,38 @@ def test_bf16_serving_mode(cuda_device, plain_gemm):
     assert pc.rel_err(whole[clear], ref[clear]) < 3 * least + 1e-3
 
 
+@pytest.mark.parametrize("heads,dim,rot_dim,vdim,kv_rank", [(6, 16, 16, 24, 32), (16, 32, 32, 32, 128), (3, 8, 48, 8, 16), (20, 16, 16, 16, 240)])
+def test_tensor_core_latent_attention(cuda_device, heads, dim, rot_dim, vdim, kv_rank):
+    """bf16 with latent and rotated sizes that are multiples of 16: the heads of a token are stacked into the rows of
+    mma.sync products over the shared key rows (a tile of sixteen stacked rows may span several tokens or a part of
+    one), for prompt portions and for single decoded tokens.  Peaked scores and strong sinks, 330 tokens over five page
+    borders; against the CUDA-core kernel on the same cache (they differ by the bf16 rounding of the softmax weights)
+    and against the oracle."""
+    config = pc.model([pc.latent(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=32, scale=0.6)], width=64)
+    wt = pc.weights(config, 9)
+    wt["l0.mix.sink"] = pc.bf16_round(wt["l0.mix.sink"] * 3.0 + 4.0)
+    toks = pc.tokens_for(config, 330, seed=3)
+    ref = pc.oracle_logits(config, wt, toks)
+    eng = pc.build_engine(config, wt, torch.bfloat16, cuda_device, prefill_chunk=512)
+    assert eng.lib.prl_attn_latent_fits(kv_rank + rot_dim, kv_rank, 64)
+    plans = ([330], [63, 17, 16, 130, 65, 20, 3, 2], [300])                 # the rest one by one: the decode-shaped kernel
+    fast = [pc.stream_logits(eng, toks, p) for p in plans]
+    eng.force_plain_attn = True
+    plain = [pc.stream_logits(eng, toks, p) for p in plans]
+    for f, p in zip(fast, plain):
+        assert pc.rel_err(f, p) < 0.25 * BF16_TOL
+        assert pc.rel_err(f, ref) < BF16_TOL and pc.rel_err(p, ref) < BF16_TOL
+    # a mixed batch: a portion beside single tokens of other sequences
+    eng.force_plain_attn = False
+    a, b, c = eng.open_stream(), eng.open_stream(), eng.open_stream()
+    eng.feed([(b, toks[:70], []), (c, toks[:129], [])])
+    got = eng.feed([(a, toks[:100], list(range(100))), (b, toks[70:71], [0]), (c, toks[129:130], [0])]).double().cpu()
+    assert pc.rel_err(got[:100], ref[:100]) < BF16_TOL and pc.rel_err(got[100:101], ref[70:71]) < BF16_TOL
+    assert pc.rel_err(got[101:], ref[129:130]) < BF16_TOL
+    for s in (a, b, c):
+        eng.close_stream(s)
+
+
 def test_long_decoding(cuda_device):
     """A short prompt and 400 single tokens over six page borders, in fp32 against the oracle."""
     config = pc.model([pc.latent(mlp=pc.moe()), pc.delta()], loop=(0, 2, 2), streams=2)

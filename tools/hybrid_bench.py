@@ -65,6 +65,23 @@ def belelorn_config(s):
                 loop=dict(start=0, stop=2, times=2))
 
 
+def pametar_config(s):
+    """Six layers of which the first two run twice (eight layer runs, the depth of the models beside it): latent attention
+    (head size 128 + 64 rotated channels, latent of 256, query latent of 3/8 width) alternating with a delta-rule memory
+    (heads of 64), every layer with routed experts of the same active width as the dense ff (four of sixteen experts of
+    ff / 4), four residual streams, a token-pair table."""
+    W, ff = s["width"], s["ff"]
+    att = dict(type="latent_attention",
+               mixer=dict(heads=s["heads"], dim=128, rot_dim=64, vdim=128, kv_rank=256, q_rank=3 * W // 8,
+                          rot=dict(dims=64, base=1e4), scale=192 ** -0.5))
+    mem = dict(type="general_delta", mixer=dict(heads=W // 64, dim=64, rank=64))
+    routed = dict(kind="moe", router=dict(experts=16, top=4, scale=1.0), expert=dict(ff=ff // 4))
+    layers = [dict(att if i % 2 == 0 else mem, mlp=routed) for i in range(s["layers"] - 2)]
+    return dict(architecture="Pametar", vocab=s["vocab"], width=W, norm=dict(eps=1e-5), streams=4,
+                embedding=dict(scale=1.0, bigram=dict(buckets=65521, mul_prev=31, mul_cur=7)), layers=layers,
+                loop=dict(start=0, stop=2, times=2))
+
+
 def peaks():
     try:
         p = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -483,6 +500,133 @@ def run_belelorn(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=T
     return res
 
 
+def run_pametar(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True, others=True):
+    """Pametar beside Belelorn (the closest design: attention + recurrent mixers, routed experts, a repeated block) and
+    the Qwen2 engine at equal width / depth / active ff / attention heads."""
+    from pipelinerl_b200.engine import DecodeEngine
+    from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
+    from pipelinerl_b200.model import ModelConfig, ParamArena
+    dev = torch.device("cuda:0")
+    timer = Timer()
+    res = {}
+    for name in sizes:
+        s = SIZES[name]
+        kw = dict(max_batch=batch, max_seq_len=max(prompt, context) + 256, max_new_tokens=warm + steps + 8, device=dev,
+                  prefill_chunk=1024)
+        entry = {}
+        if e2e and others:
+            qcfg = ModelConfig(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"], num_layers=s["layers"],
+                               num_q_heads=s["heads"], num_kv_heads=s["kv"])
+            eng = DecodeEngine(qcfg, ParamArena(qcfg, dev).init_random(seed=1), **kw)
+            entry["qwen2"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["qwen2"]["params_M"] = round(qcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+            bcfg = HybridConfig.from_belelorn(belelorn_config(s))
+            eng = HybridEngine(bcfg, ParamArena(bcfg, dev).init_random(seed=1), **kw)
+            entry["belelorn"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["belelorn"]["params_M"] = round(bcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+        pcfg = HybridConfig.from_pametar(pametar_config(s))
+        eng = HybridEngine(pcfg, ParamArena(pcfg, dev).init_random(seed=1), **kw)
+        if e2e:
+            entry["pametar"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["pametar"]["params_M"] = round(pcfg.num_params() / 1e6)
+            for other in ("qwen2", "belelorn"):
+                if other in entry:
+                    entry[f"pametar_over_{other}"] = {k: round(entry["pametar"][f"{k}_tokens_per_s"] / entry[other][f"{k}_tokens_per_s"], 3)
+                                                      for k in ("prefill", "decode")}
+        if kernels:
+            entry["kernels"] = kernel_table_pametar(eng, s, batch, 1024, timer)
+        res[name] = entry
+        del eng
+        torch.cuda.empty_cache()
+    return res
+
+
+def kernel_table_pametar(eng, s, batch, chunk, timer):
+    """The parts of a Pametar layer alone, at the decode shape (`batch` one-token segments at position 2047) and the
+    prefill shape (one segment of `chunk` rows whose sequence already holds `chunk` tokens): the engine's own mixer and
+    feed-forward methods on its buffers, then single kernels; memory-bound ones against the measured copy bandwidth, the
+    attention product against the measured bf16 GEMM rate, the recurrence against the SMs' fp32 FMA rate."""
+    from pipelinerl_b200 import _lib
+    from pipelinerl_b200.cache import PAGE_SIZE
+    from pipelinerl_b200.hybrid import _Rows
+    lib, cfg = eng.lib, eng.cfg
+    hbm, tflops, how = peaks()
+    fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+    W, S = cfg.width, cfg.streams
+    ai = next(i for i, L in enumerate(cfg.layers) if L.kind == "latent")
+    di = next(i for i, L in enumerate(cfg.layers) if L.kind == "delta")
+    A, D = cfg.layers[ai], cfg.layers[di]
+    a, c, e = A.latent, D.delta, A.mlp.moe
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "fp32_fma_tflops": round(fma_tflops, 1), "source": how}}
+    i32 = dict(dtype=torch.int32, device=eng.dev)
+    ctx = 2047
+    pages_per = (ctx + PAGE_SIZE) // PAGE_SIZE
+    for b in range(batch):
+        eng.block_table[b, :pages_per].copy_(torch.arange(1 + b * pages_per, 1 + (b + 1) * pages_per, **i32))
+    for pool in eng.lat_pool.values():
+        pool.normal_(0, 0.5)
+    for shape, n, ns in (("decode", batch, batch), ("prefill", chunk, 1)):
+        R = _Rows(eng, n)
+        R.P.normal_(0, 0.5); R.xa.normal_(0, 0.5); R.xs.normal_(0, 0.5)
+        pos0 = ctx if shape == "decode" else chunk
+        if shape == "decode":
+            R.seg.copy_(torch.stack([torch.arange(n, **i32), torch.ones(n, **i32), torch.full((n,), ctx, **i32), torch.arange(n, **i32)]))
+            R.row_slot.copy_(torch.arange(n, **i32)); R.row_pos.fill_(ctx)
+        else:
+            R.seg[:, :1].copy_(torch.tensor([[0], [n], [pos0], [0]], **i32))
+            R.row_slot.zero_(); R.row_pos.copy_(torch.arange(pos0, pos0 + n, **i32)); R.row_back.copy_(torch.arange(n, **i32))
+        R.tokens.copy_(torch.randint(0, cfg.vocab_size, (n,), device=eng.dev).int())
+        eng._st = _lib.stream_ptr()
+        segs = (R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr(), ns)
+        max_q = 1 if shape == "decode" else n
+        wa, wd = f"l{A.weights_of}.", f"l{D.weights_of}."
+        keys = (ctx + 1) * n if shape == "decode" else n * pos0 + n * (n + 1) // 2      # (query, key) pairs
+        kd = a.kv_rank + a.rot_dim
+        t = {}
+        t["latent_mixer"] = timer.events(lambda: eng._latent_mixer(R, n, ai, A, wa, segs, max_q, R.row_pos, R.seg[2]))
+        t["delta_mixer"] = timer.events(lambda: eng._delta_mixer(R, n, di, D, wd, segs))
+        t["routed_ff"] = timer.events(lambda: eng._routed_ff(R, n, wa, e, 1.0))
+        t["stream_close"] = timer.events(lambda: eng._stream_close(R, n, ai, "1", R.y0, 1, R.P.data_ptr(), W))
+        t["embed_pair"] = timer.events(lambda: eng._embed(R, n, R.tokens, R.row_pos, ns))
+        pool = eng.lat_pool[ai].data_ptr()
+
+        def attn():
+            _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, 0, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE,
+                                             *segs[:2], R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, 1, kd, a.kv_rank, a.scale, 0, 0,
+                                             0.0, eng.vec[wa + "mix.sink"].data_ptr(), 1, R.ya.data_ptr(), eng._st))
+        t["latent_attention"] = timer.events(attn)
+        nq = c.heads * c.dim
+
+        def scan():
+            _lib.check(lib.prl_delta_scan(R.P.data_ptr(), 5 * nq + c.rank + W, 0, nq, 2 * nq, 4 * nq, R.aux.data_ptr(), nq,
+                                          eng.vec[wd + "mix.w0"].data_ptr(), eng.vec[wd + "mix.a.b"].data_ptr(), c.decay_scale,
+                                          c.unit_eps, c.heads, c.dim, c.dim, *segs[:3], ns, eng.delta_state[di].data_ptr(),
+                                          R.o.data_ptr(), nq, eng._st))
+        t["delta_scan"] = timer.events(scan)
+        row = {k: {"us": round(v * 1e3, 1)} for k, v in t.items()}
+        attn_flops = 2.0 * keys * a.heads * (kd + a.kv_rank)
+        row["latent_attention"]["tflops"] = round(attn_flops / t["latent_attention"] / 1e9, 1)
+        row["latent_attention"]["of_bf16_peak"] = round(attn_flops / t["latent_attention"] / 1e9 / tflops, 3)
+        if shape == "decode":
+            cache = n * (ctx + 1) * kd * 2
+            row["latent_attention"]["of_hbm"] = round(cache / t["latent_attention"] / 1e6 / hbm, 3)
+            state = 2 * n * c.heads * c.dim * c.dim * 4
+            row["delta_scan"]["of_hbm"] = round(state / t["delta_scan"] / 1e6 / hbm, 3)
+        else:
+            row["delta_scan"]["of_fp32_fma"] = round(n * c.heads * c.dim * c.dim * 5 * 2 / t["delta_scan"] / 1e9 / fma_tflops, 3)
+        stream_bytes = n * W * 4 * (2 * S + 2) + n * W * 2
+        row["stream_close"]["of_hbm"] = round(stream_bytes / t["stream_close"] / 1e6 / hbm, 3)
+        out[shape] = row
+        del R
+    eng.block_table.zero_()
+    eng.states.reset(0)
+    return out
+
+
 def run(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True):
     from pipelinerl_b200.engine import DecodeEngine
     from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
@@ -529,12 +673,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--only-kernels", action="store_true", help="skip the end-to-end runs (a small case for a profiler)")
-    ap.add_argument("--design", default="povurax", choices=["povurax", "belelorn"], help="which hybrid design is measured")
+    ap.add_argument("--design", default="povurax", choices=["povurax", "belelorn", "pametar"], help="which hybrid design is measured")
     ap.add_argument("--alone", action="store_true", help="--design belelorn: skip the Qwen2 and Povurax runs beside it")
     a = ap.parse_args()
     from pipelinerl_b200 import _lib
     before = _lib.launch_count()
-    if a.design == "belelorn":
+    if a.design == "pametar":
+        res = run_pametar(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels,
+                          e2e=not a.only_kernels, others=not a.alone)
+    elif a.design == "belelorn":
         res = run_belelorn(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels,
                            e2e=not a.only_kernels, others=not a.alone)
     else:
