@@ -774,12 +774,14 @@ int prl_latent_query(const float* Q, int64_t ldq, int32_t n, int32_t H, int32_t 
 int prl_store_groups(const float* src, int64_t lds, int32_t n, int32_t G, int32_t C, void* out, int64_t ld_out, int32_t f32,
                      prl_stream_t stream);
 /* S_t = diag(w_t) S_(t-1) - (a_t u_t)(u_t^T S_(t-1)) + k_t v_t^T, o_t = S_t^T r_t;  u = k / sqrt(sum k^2 + unit_eps),
- * w = exp(-decay_scale sigmoid(zw + w_bias)), a = sigmoid(P[off_a] + a_bias);  state [slot][head][dv][dk] fp32 */
+ * w = exp(-decay_scale sigmoid(zw + w_bias)), a = sigmoid(P[off_a] + a_bias);  state [slot][head][dv][dk] fp32.  The
+ * removal logits in P and the decay logits in zw are overwritten (by a u and w), the unit keys go to `unit_keys` */
 int64_t prl_delta_state_floats(int32_t heads, int32_t dk, int32_t dv);
-int prl_delta_scan(const float* P, int64_t ldp, int32_t off_r, int32_t off_k, int32_t off_v, int32_t off_a, const float* zw,
-                   int64_t ldw, const float* w_bias, const float* a_bias, float decay_scale, float unit_eps, int32_t heads,
-                   int32_t dk, int32_t dv, const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_slot,
-                   int32_t n_seg, float* state, float* out, int64_t ld_out, prl_stream_t stream);
+int prl_delta_scan(float* P, int64_t ldp, int32_t off_r, int32_t off_k, int32_t off_v, int32_t off_a, float* zw, int64_t ldw,
+                   const float* w_bias, const float* a_bias, float decay_scale, float unit_eps, int32_t heads, int32_t dk,
+                   int32_t dv, int32_t n_rows, float* unit_keys /* scratch [n_rows][heads*dk] */, const int32_t* seg_start,
+                   const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg, int32_t max_len /* longest segment, 0 =
+                   unknown */, float* state, float* out, int64_t ld_out, prl_stream_t stream);
 /* x = embed[token] * scale + pair[(prev * mul_prev + token * mul_cur) mod buckets] (row `buckets` at position 0; pair NULL:
  * no such table); all S streams of the row start as x; ha = T(tanh(alpha * sum_s w_in[s] x) * gain + shift) */
 int prl_embed_pair(const int32_t* tokens, const int32_t* row_pos, const int32_t* row_slot, const int32_t* row_back,

@@ -97,8 +97,19 @@ __global__ void streams_open_kernel(const float* __restrict__ xs, const int32_t*
   }
 }
 
-template <typename T>
-__global__ void streams_close_kernel(const float* __restrict__ y, int64_t ldy, int n_split, int64_t split_stride,
+template <typename T> __device__ __forceinline__ void st4(T* p, int64_t i, const float (&v)[4]);
+template <> __device__ __forceinline__ void st4<float>(float* p, int64_t i, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p + i) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p + i) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// V consecutive channels per thread (V = 4: 128-bit loads and stores; every row stride and base a multiple of 4 floats).
+// A channel's arithmetic is the same for both widths.
+template <typename T, int V, int SMAX>
+__global__ void __launch_bounds__(512) streams_close_kernel(const float* __restrict__ y, int64_t ldy, int n_split, int64_t split_stride,
                                      const float* __restrict__ scale, const float* __restrict__ gate, int64_t ldg,
                                      const float* __restrict__ gate_bias, const float* __restrict__ mix,
                                      const float* __restrict__ w_out, int S, int W, float* __restrict__ xs,
@@ -115,27 +126,54 @@ __global__ void streams_close_kernel(const float* __restrict__ y, int64_t ldy, i
   }
   __syncthreads();
   const float alpha = next_in ? nm.alpha[0] : 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float v = 0.f;
-    for (int k = 0; k < n_split; ++k) v += y[k * split_stride + r * ldy + c];       // slices in order
-    if (scale) v *= scale[c];
-    if (gate) v *= sigmoid_f(gate[r * ldg + c] + (gate_bias ? gate_bias[c] : 0.f));
-    float old[kMaxStreams];
+  for (int c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    float v[V], old[SMAX][V], h[V];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) old[s] = s < S ? xs[(r * S + s) * W + c] : 0.f;
-    float u = 0.f;
-#pragma unroll
-    for (int t = 0; t < kMaxStreams; ++t) {
-      if (t >= S) break;
-      float a = 0.f;
-#pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
-        if (s < S) a = fmaf(sm_mix[s * S + t], old[s], a);
-      a = fmaf(sm_out[t], v, a);
-      xs[(r * S + t) * W + c] = a;
-      u = fmaf(sm_in[t], a, u);
+    for (int e = 0; e < V; ++e) v[e] = 0.f;
+    for (int k = 0; k < n_split; ++k) {                               // slices in order
+      const float* p = y + k * split_stride + r * ldy + c;
+      if constexpr (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w; }
+      else v[0] += p[0];
     }
-    if (next_in) stf(ha, r * W + c, tanhf(alpha * u) * nm.gain[c] + nm.shift[c]);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      if (scale) v[e] *= scale[c + e];
+      if (gate) v[e] *= sigmoid_f(gate[r * ldg + c + e] + (gate_bias ? gate_bias[c + e] : 0.f));
+    }
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) {
+      if (s < S) {
+        const float* p = xs + (r * S + s) * W + c;
+        if constexpr (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); old[s][0] = t.x; old[s][1] = t.y; old[s][2] = t.z; old[s][3] = t.w; }
+        else old[s][0] = p[0];
+      }
+    }
+    float u[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) u[e] = 0.f;
+#pragma unroll
+    for (int t = 0; t < SMAX; ++t) {
+      if (t >= S) break;
+      float a[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        a[e] = 0.f;
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < S) a[e] = fmaf(sm_mix[s * S + t], old[s][e], a[e]);
+        a[e] = fmaf(sm_out[t], v[e], a[e]);
+        u[e] = fmaf(sm_in[t], a[e], u[e]);
+      }
+      float* p = xs + (r * S + t) * W + c;
+      if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(a[0], a[1], a[2], a[3]);
+      else p[0] = a[0];
+    }
+    if (next_in) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) h[e] = tanhf(alpha * u[e]) * nm.gain[c + e] + nm.shift[c + e];
+      if constexpr (V == 4) st4(ha, r * W + c, h);
+      else stf(ha, r * W + c, h[0]);
+    }
   }
 }
 
@@ -192,9 +230,14 @@ extern "C" int prl_streams_close(const float* y, int64_t ldy, int32_t n_split, i
   PRL_CHECK_ARG(!next_in || (next_alpha && next_gain && next_shift && ha), "prl_streams_close: the next norm is incomplete");
   PRL_CHECK_ARG(!gate || ldg >= W, "prl_streams_close: bad gate stride");
   TanhNorm nm{next_alpha, next_gain, next_shift};
-  const int th = row_threads(W) < 96 ? 96 : row_threads(W);     // at least S*S + S threads fill the shared tables
-  if (f32) PRL_CUDA(launch_pdl(streams_close_kernel<float>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, y, ldy, n_split, split_stride, scale, gate, ldg, gate_bias, mix, w_out, S, W, xs, next_in, nm, (float*)ha));
-  else PRL_CUDA(launch_pdl(streams_close_kernel<bf16>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, y, ldy, n_split, split_stride, scale, gate, ldg, gate_bias, mix, w_out, S, W, xs, next_in, nm, (bf16*)ha));
+  const bool v4 = S <= 4 && W % 4 == 0 && ldy % 4 == 0 && split_stride % 4 == 0 && (!gate || ldg % 4 == 0) && ((uintptr_t)y & 15) == 0 &&
+                  ((uintptr_t)xs & 15) == 0 && (!gate || ((uintptr_t)gate & 15) == 0) && (!ha || ((uintptr_t)ha & 15) == 0);
+  int th = v4 ? (W / 4 + 31) / 32 * 32 : row_threads(W);
+  th = th > 512 ? 512 : (th < 96 ? 96 : th);                    // at least S*S + S threads fill the shared tables
+#define PRL_CLOSE(TT, VV, SS) PRL_CUDA(launch_pdl((streams_close_kernel<TT, VV, SS>), dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, y, ldy, n_split, split_stride, scale, gate, ldg, gate_bias, mix, w_out, S, W, xs, next_in, nm, (TT*)ha))
+  if (f32) { if (S > 4) PRL_CLOSE(float, 1, kMaxStreams); else if (v4) PRL_CLOSE(float, 4, 4); else PRL_CLOSE(float, 1, 4); }
+  else { if (S > 4) PRL_CLOSE(bf16, 1, kMaxStreams); else if (v4) PRL_CLOSE(bf16, 4, 4); else PRL_CLOSE(bf16, 1, 4); }
+#undef PRL_CLOSE
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

@@ -680,7 +680,7 @@ class _Rows:
                 c = L.delta
                 nq = c.heads * c.dim
                 wide_p = max(wide_p, 5 * nq + c.rank + (W if L.gated else 0))
-                wide_aux, wide_o = max(wide_aux, nq), max(wide_o, nq)
+                wide_aux, wide_o, wide_o2 = max(wide_aux, nq), max(wide_o, nq), max(wide_o2, nq)
             else:
                 a, s = L.attn, L.ssd
                 nq = a.heads * a.dim
@@ -1219,7 +1219,7 @@ class HybridEngine(EngineCore):
             if L.kind == "latent":
                 y, k, gate, ldg = self._latent_mixer(R, n, i, L, w, segs, max_q, row_pos, seg_pos0)
             else:
-                y, k, gate, ldg = self._delta_mixer(R, n, i, L, w, segs)
+                y, k, gate, ldg = self._delta_mixer(R, n, i, L, w, segs, max_q)
             self._stream_close(R, n, i, "1", y, k, gate, ldg)
             if L.mlp is not None:
                 gate = None
@@ -1253,10 +1253,9 @@ class HybridEngine(EngineCore):
         self._mm(R.ya, a.q_rank, w + "mix.uq", hq, R.aux, n)
         _lib.check(lib.prl_latent_query(R.aux.data_ptr(), hq, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(),
                                         row_pos.data_ptr(), R.yb.data_ptr(), R.q.data_ptr(), f32, st))
-        # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers
+        # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers, into the attention query
         self._mm_heads(R.yb, H * a.dim, a.dim, self.uk_t[L.weights_of].data_ptr(), a.dim, rk * a.dim, n, rk, a.dim,
-                       R.o, H * rk, rk, H)
-        _lib.check(lib.prl_store_groups(R.o.data_ptr(), H * rk, n, H, rk, R.q.data_ptr(), kd, f32, st))
+                       R.o, H, R.q, H * kd, kd)
         pool = self.lat_pool[i].data_ptr()
         sink = vec[w + "mix.sink"].data_ptr() if a.sink else None
         if not self.f32 and not self.force_plain_attn and lib.prl_attn_latent_fits(kd, rk, PAGE_SIZE):
@@ -1270,20 +1269,28 @@ class HybridEngine(EngineCore):
                                              rk, a.scale, 0, 0, 0.0, sink, 1, R.ya.data_ptr(), st))
         # v[h] = W_uv,h o_lat[h], then the output projection over the concatenated heads
         self._mm_heads(R.ya, H * rk, rk, self.arena.ptr(w + "mix.uv"), rk, a.vdim * rk, n, a.vdim, rk,
-                       R.o, H * a.vdim, a.vdim, H)
-        _lib.check(lib.prl_store_groups(R.o.data_ptr(), H * a.vdim, n, 1, H * a.vdim, R.yb.data_ptr(), H * a.vdim, f32, st))
+                       R.o, H, R.yb, H * a.vdim, a.vdim)
         k0 = self._mm(R.yb, H * a.vdim, w + "mix.o", W, R.y0, n, split=True)
         return R.y0, k0, (P + 4 * (a.q_rank + kd)) if L.gated else None, ld
 
-    def _mm_heads(self, src, lda, a_step, w_ptr, ldw, w_step, n, N, K, out, ldc, c_step, heads) -> None:
-        """out[:, h*c_step : +N] (fp32) = src[:, h*a_step : +K] @ W_h[N, K]^T for every head h (W_h = w_ptr + h * w_step)."""
-        f32 = int(self.f32)
-        _lib.check(self.lib.prl_gemm_any_batched(src.data_ptr(), f32, lda, a_step, w_ptr, f32, ldw, w_step, n, N, K,
-                                                 out.data_ptr(), ldc, c_step, heads, self._st))
+    def _mm_heads(self, src, lda, a_step, w_ptr, ldw, w_step, n, N, K, tmp, heads, dst, ld_dst, dst_step) -> None:
+        """dst[:, h*dst_step : +N] (operand type) = src[:, h*a_step : +K] @ W_h[N, K]^T for every head h (W_h = w_ptr +
+        h * w_step elements).  bf16 prompt batches: one tcgen05 GEMM per head writing bf16 in place; otherwise one batched
+        CUDA-core launch into the fp32 buffer `tmp` and a cast."""
+        lib, st, f32 = self.lib, self._st, int(self.f32)
+        if (not self.f32 and not self.force_plain_gemm and n > 128 and K >= 16 and K % 8 == 0 and lda % 8 == 0 and ldw % 8 == 0
+                and a_step % 8 == 0 and w_step % 8 == 0 and ld_dst % 8 == 0 and dst_step % 8 == 0):
+            for h in range(heads):
+                _lib.check(lib.prl_gemm_tn(src.data_ptr() + 2 * h * a_step, lda, w_ptr + 2 * h * w_step, ldw, n, N, K,
+                                           dst.data_ptr() + 2 * h * dst_step, ld_dst, 0, 0, None, None, 0, 1.0, st))
+            return
+        _lib.check(lib.prl_gemm_any_batched(src.data_ptr(), f32, lda, a_step, w_ptr, f32, ldw, w_step, n, N, K,
+                                            tmp.data_ptr(), heads * N, N, heads, st))
+        _lib.check(lib.prl_store_groups(tmp.data_ptr(), heads * N, n, heads, N, dst.data_ptr(), dst_step, f32, st))
 
-    def _delta_mixer(self, R, n, i, L, w, segs):
+    def _delta_mixer(self, R, n, i, L, w, segs, max_q=0):
         """Delta-rule memory: one projection [r | k | v | g | a | w1 | gate]; the decay logits come through the tanh
-        bottleneck in fp32; prl_delta_scan forms the unit key, decay and removal rate itself and walks the tokens."""
+        bottleneck in fp32; prl_delta_scan forms the unit key (into o2), decay and removal rate and walks the tokens."""
         c, lib, st, vec, f32, W = L.delta, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
         seg_start, seg_len, seg_slot, ns = segs
         nq = c.heads * c.dim
@@ -1294,8 +1301,9 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_gemm_any(P + 4 * 5 * nq, 1, ld, self.arena.ptr(w + "mix.w2"), f32, c.rank, n, nq, c.rank,
                                     R.aux.data_ptr(), nq, st))
         _lib.check(lib.prl_delta_scan(P, ld, 0, nq, 2 * nq, 4 * nq, R.aux.data_ptr(), nq, vec[w + "mix.w0"].data_ptr(),
-                                      vec[w + "mix.a.b"].data_ptr(), c.decay_scale, c.unit_eps, c.heads, c.dim, c.dim,
-                                      seg_start, seg_len, seg_slot, ns, self.delta_state[i].data_ptr(), R.o.data_ptr(), nq, st))
+                                      vec[w + "mix.a.b"].data_ptr(), c.decay_scale, c.unit_eps, c.heads, c.dim, c.dim, n,
+                                      R.o2.data_ptr(), seg_start, seg_len, seg_slot, ns, max_q, self.delta_state[i].data_ptr(),
+                                      R.o.data_ptr(), nq, st))
         _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, nq, P + 4 * 3 * nq, ld, vec[w + "mix.norm"].data_ptr(), nq, c.dim, n,
                                      nq, 1, 0, 1, self.cfg.eps, R.ya.data_ptr(), f32, st))
         k0 = self._mm(R.ya, nq, w + "mix.o", W, R.y0, n, split=True)

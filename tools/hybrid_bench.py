@@ -588,23 +588,29 @@ def kernel_table_pametar(eng, s, batch, chunk, timer):
         kd = a.kv_rank + a.rot_dim
         t = {}
         t["latent_mixer"] = timer.events(lambda: eng._latent_mixer(R, n, ai, A, wa, segs, max_q, R.row_pos, R.seg[2]))
-        t["delta_mixer"] = timer.events(lambda: eng._delta_mixer(R, n, di, D, wd, segs))
+        t["delta_mixer"] = timer.events(lambda: eng._delta_mixer(R, n, di, D, wd, segs, max_q))
         t["routed_ff"] = timer.events(lambda: eng._routed_ff(R, n, wa, e, 1.0))
         t["stream_close"] = timer.events(lambda: eng._stream_close(R, n, ai, "1", R.y0, 1, R.P.data_ptr(), W))
         t["embed_pair"] = timer.events(lambda: eng._embed(R, n, R.tokens, R.row_pos, ns))
         pool = eng.lat_pool[ai].data_ptr()
 
         def attn():
+            _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE, *segs[:2],
+                                           R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, kd, a.kv_rank, a.scale,
+                                           eng.vec[wa + "mix.sink"].data_ptr(), R.ya.data_ptr(), eng._st))
+
+        def attn_plain():
             _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, 0, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE,
                                              *segs[:2], R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, 1, kd, a.kv_rank, a.scale, 0, 0,
                                              0.0, eng.vec[wa + "mix.sink"].data_ptr(), 1, R.ya.data_ptr(), eng._st))
         t["latent_attention"] = timer.events(attn)
+        t["latent_attention_cuda_cores"] = timer.events(attn_plain, iters=3, warm=1)
         nq = c.heads * c.dim
 
         def scan():
             _lib.check(lib.prl_delta_scan(R.P.data_ptr(), 5 * nq + c.rank + W, 0, nq, 2 * nq, 4 * nq, R.aux.data_ptr(), nq,
                                           eng.vec[wd + "mix.w0"].data_ptr(), eng.vec[wd + "mix.a.b"].data_ptr(), c.decay_scale,
-                                          c.unit_eps, c.heads, c.dim, c.dim, *segs[:3], ns, eng.delta_state[di].data_ptr(),
+                                          c.unit_eps, c.heads, c.dim, c.dim, n, R.o2.data_ptr(), *segs[:3], ns, max_q, eng.delta_state[di].data_ptr(),
                                           R.o.data_ptr(), nq, eng._st))
         t["delta_scan"] = timer.events(scan)
         row = {k: {"us": round(v * 1e3, 1)} for k, v in t.items()}
