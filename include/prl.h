@@ -755,10 +755,14 @@ int prl_attn_any_sink(const void* q, const void* k_pool, const void* v_pool, int
  * channels of the key rows, optional per-head sink logit; out bf16 [n][H][rank].  prl_attn_latent_fits says whether the
  * geometry is built (kd, rank multiples of 16, rank <= 256, pages of a multiple of 32 tokens) */
 int32_t prl_attn_latent_fits(int32_t kd, int32_t rank, int32_t page_size);
+int32_t prl_attn_latent_splits(int32_t n_seg, int32_t H);
+size_t prl_attn_latent_workspace_bytes(int32_t n_seg, int32_t H, int32_t rank);
+/* ws (may be NULL): fp32 workspace of prl_attn_latent_workspace_bytes(n_seg, H, rank) bytes; with it a batch of single
+ * tokens spreads each sequence's keys over several CTAs whose shares a second launch merges */
 int prl_attn_latent(const void* q, const void* pool, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
                     const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_pos0, const int32_t* seg_slot,
                     int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank, float scale, const float* sink,
-                    void* out, prl_stream_t stream);
+                    void* out, void* ws, size_t ws_bytes, prl_stream_t stream);
 /* query latent cq = rmsnorm(P[off_q : off_q + q_rank]) * q_gain (operand type) and the latent cache row
  * [rmsnorm(P[off_kv : +rank]) * kv_gain | rotate_half(P[off_kv + rank : +rot], pos)] -> pool[page][page_size][rank + rot] */
 int prl_latent_prep(const float* P, int64_t ldp, int32_t off_q, int32_t q_rank, int32_t off_kv, int32_t rank, int32_t rot,

@@ -248,10 +248,10 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int page_size, const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
     const int32_t* __restrict__ seg_pos0, const int32_t* __restrict__ seg_slot, int H, int kd, int rank, float scale,
-    const float* __restrict__ sink, bf16* __restrict__ out) {
+    const float* __restrict__ sink, bf16* __restrict__ out, int splits, float* __restrict__ ws) {
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int seg = blockIdx.y;
+  const int seg = blockIdx.y, z = blockIdx.z;
   if (seg_len[seg] != 1) return;
   const int m_total = H, m0 = blockIdx.x * 16;
   const int ld = kd + kPadH, ch = kd / 8;
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
   const int n_tiles = pos_tok / kKeys + 1;
   Acc<NV> acc;
   acc.init();
-  for (int t = warp; t < n_tiles; t += kSplitWarps) {
+  for (int t = z * kSplitWarps + warp; t < n_tiles; t += kSplitWarps * splits) {     // CTA z of `splits` takes every splits-th round
     __syncwarp();
     stage_keys(Ks, ld, pool, bt, page_size, kd, t * kKeys, pos_tok, lane, 32);
     cp_commit();
@@ -297,18 +297,65 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
     if ((lane & 3) == 0) { pr[rank] = acc.m[i]; pr[rank + 1] = acc.l[i]; }
   }
   __syncthreads();
-  for (int e = tid; e < m_here * rank; e += blockDim.x) {              // merge in warp order
-    const int r = e / rank, c = e - r * rank;
-    float mx = sink ? sink[(m0 + r) % H] : kNegBig;
+  const bool last = splits == 1;                                       // else: this CTA's share goes to the workspace unnormalised
+  float* wsp = ws ? ws + (((int64_t)seg * gridDim.x + blockIdx.x) * splits + z) * 16 * ps : nullptr;
+  __shared__ float row_w[16][kSplitWarps + 2];                         // per row: the warps' weights | max | denominator
+  if (tid < m_here) {                                                  // merge in warp order
+    const int r = tid;
+    float mx = (sink && last) ? sink[(m0 + r) % H] : kNegBig;
     for (int w = 0; w < kSplitWarps; ++w) mx = fmaxf(mx, part[((int64_t)w * 16 + r) * ps + rank]);
-    float num = 0.f, den = sink ? expf(sink[(m0 + r) % H] - mx) : 0.f;
+    float den = (sink && last) ? expf(sink[(m0 + r) % H] - mx) : 0.f;
     for (int w = 0; w < kSplitWarps; ++w) {
       const float* pr = part + ((int64_t)w * 16 + r) * ps;
       const float wgt = expf(pr[rank] - mx);                           // a warp without tiles: exp(-1e30 - mx) = 0
-      num = fmaf(wgt, pr[c], num);
+      row_w[r][w] = wgt;
       den = fmaf(wgt, pr[rank + 1], den);
     }
-    out[(row0 * H + m0 + r) * rank + c] = __float2bfloat16_rn(num / den);
+    row_w[r][kSplitWarps] = mx;
+    row_w[r][kSplitWarps + 1] = den;
+    if (!last) { wsp[r * ps + rank] = mx; wsp[r * ps + rank + 1] = den; }
+  }
+  __syncthreads();
+  for (int e = tid; e < m_here * rank; e += blockDim.x) {
+    const int r = e / rank, c = e - r * rank;
+    float num = 0.f;
+#pragma unroll
+    for (int w = 0; w < kSplitWarps; ++w) num = fmaf(row_w[r][w], part[((int64_t)w * 16 + r) * ps + c], num);
+    if (last) out[(row0 * H + m0 + r) * rank + c] = __float2bfloat16_rn(num / row_w[r][kSplitWarps + 1]);
+    else wsp[r * ps + c] = num;
+  }
+}
+
+// The shares of the `splits` CTAs of a work unit, [seg][unit][split][16][rank + 2] = o | m | l, into the output.
+__global__ void attn_latent_merge_kernel(const float* __restrict__ ws, const int32_t* __restrict__ seg_start,
+                                         const int32_t* __restrict__ seg_len, int H, int rank, int splits,
+                                         const float* __restrict__ sink, bf16* __restrict__ out) {
+  pdl_wait();
+  const int seg = blockIdx.y, unit = blockIdx.x;
+  if (seg_len[seg] != 1) return;
+  const int ps = rank + 2, m0 = unit * 16, m_here = min(16, H - m0);
+  const int64_t row0 = seg_start[seg];
+  const float* base = ws + ((int64_t)seg * gridDim.x + unit) * splits * 16 * ps;
+  __shared__ float row_w[16][8 + 1];                                   // per row: the shares' weights | 1 / denominator
+  if ((int)threadIdx.x < m_here) {
+    const int r = threadIdx.x;
+    float mx = sink ? sink[m0 + r] : kNegBig;
+    for (int zz = 0; zz < splits; ++zz) mx = fmaxf(mx, base[((int64_t)zz * 16 + r) * ps + rank]);
+    float den = sink ? expf(sink[m0 + r] - mx) : 0.f;
+    for (int zz = 0; zz < splits; ++zz) {
+      const float* pr = base + ((int64_t)zz * 16 + r) * ps;
+      const float wgt = expf(pr[rank] - mx);
+      row_w[r][zz] = wgt;
+      den = fmaf(wgt, pr[rank + 1], den);
+    }
+    row_w[r][8] = 1.f / den;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < m_here * rank; e += blockDim.x) {
+    const int r = e / rank, c = e - r * rank;
+    float num = 0.f;
+    for (int zz = 0; zz < splits; ++zz) num = fmaf(row_w[r][zz], base[((int64_t)zz * 16 + r) * ps + c], num);
+    out[(row0 * H + m0 + r) * rank + c] = __float2bfloat16_rn(num * row_w[r][8]);
   }
 }
 
@@ -330,10 +377,20 @@ extern "C" int32_t prl_attn_latent_fits(int32_t kd, int32_t rank, int32_t page_s
          split_smem(kd, rank) <= 200 * 1024;
 }
 
+// Key splits of the decode-shaped kernel and the fp32 workspace they need: enough CTAs to cover the SMs, at most 8
+extern "C" int32_t prl_attn_latent_splits(int32_t n_seg, int32_t H) {
+  const int units = n_seg * ((H + 15) / 16);
+  int s = num_sms() / (units > 0 ? units : 1);
+  return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
+extern "C" size_t prl_attn_latent_workspace_bytes(int32_t n_seg, int32_t H, int32_t rank) {
+  return (size_t)n_seg * ((H + 15) / 16) * prl_attn_latent_splits(n_seg, H) * 16 * (rank + 2) * sizeof(float);
+}
+
 extern "C" int prl_attn_latent(const void* q, const void* pool, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
                                const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_pos0,
                                const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank,
-                               float scale, const float* sink, void* out, prl_stream_t stream) {
+                               float scale, const float* sink, void* out, void* ws, size_t ws_bytes, prl_stream_t stream) {
   PRL_CHECK_ARG(q && pool && block_table && seg_start && seg_len && seg_pos0 && seg_slot && out, "prl_attn_latent: NULL argument");
   PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && max_blocks >= 1 && prl_attn_latent_fits(kd, rank, page_size),
                 "prl_attn_latent: geometry kd=%d rank=%d page=%d is not built (see prl_attn_latent_fits)", kd, rank, page_size);
@@ -346,22 +403,34 @@ extern "C" int prl_attn_latent(const void* q, const void* pool, const int32_t* b
   do {                                                                                                                    \
     if (rank <= 64) {                                                                                                     \
       PRL_CUDA(ensure_smem(KERNEL<8>, (int)(SMEM), ATTR[0]));                                                             \
-      PRL_CUDA(launch_pdl(KERNEL<8>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo)); \
+      PRL_CUDA(launch_pdl(KERNEL<8>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
     } else if (rank <= 128) {                                                                                             \
       PRL_CUDA(ensure_smem(KERNEL<16>, (int)(SMEM), ATTR[1]));                                                            \
-      PRL_CUDA(launch_pdl(KERNEL<16>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo)); \
+      PRL_CUDA(launch_pdl(KERNEL<16>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
     } else {                                                                                                              \
       PRL_CUDA(ensure_smem(KERNEL<32>, (int)(SMEM), ATTR[2]));                                                            \
-      PRL_CUDA(launch_pdl(KERNEL<32>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo)); \
+      PRL_CUDA(launch_pdl(KERNEL<32>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
     }                                                                                                                     \
   } while (0)
   if (max_q == 1) {
-    dim3 grid((H + 15) / 16, n_seg);
+    int splits = prl_attn_latent_splits(n_seg, H);
+    if (!ws || ws_bytes < prl_attn_latent_workspace_bytes(n_seg, H, rank)) splits = 1;      // no room for the shares: one CTA per unit
+    float* wsf = (float*)ws;
+    dim3 grid((H + 15) / 16, n_seg, splits);
+#define EXTRA , splits, wsf
     PRL_LAT(attn_latent_split_kernel, attr_split, grid, kSplitWarps * 32, split_smem(kd, rank));
+#undef EXTRA
+    if (splits > 1) {
+      PRL_LAUNCH_CHECK();
+      PRL_CUDA(launch_pdl(attn_latent_merge_kernel, dim3((H + 15) / 16, n_seg), dim3(256), (size_t)0, st, (const float*)wsf, seg_start,
+                          seg_len, H, rank, splits, sink, oo));
+    }
   } else {
     const int64_t m_max = (int64_t)max_q * H;
     dim3 grid((unsigned)((m_max + kRowWarps * 16 - 1) / (kRowWarps * 16)), n_seg);
+#define EXTRA
     PRL_LAT(attn_latent_rows_kernel, attr_rows, grid, kRowWarps * 32, rows_smem(kd));
+#undef EXTRA
   }
 #undef PRL_LAT
   PRL_LAUNCH_CHECK();

@@ -853,6 +853,10 @@ class HybridEngine(EngineCore):
                 a = cfg.layers[i].attn
                 self.attn_splits[i] = int(lib.prl_paged_attn_splits(B, a.kv_heads, self.max_seq_len))
                 ws = max(ws, int(lib.prl_paged_attn_workspace_bytes(B, a.heads, self.attn_splits[i])))
+        for L in cfg.layers:                              # latent attention: the key splits' shares of a batch of single tokens
+            if L.kind == "latent":
+                for n_seg in range(1, max(B, 4) + 1):     # the split count falls as the batch grows; the product need not
+                    ws = max(ws, int(lib.prl_attn_latent_workspace_bytes(n_seg, L.latent.heads, L.latent.kv_rank)))
         self.attn_ws = torch.zeros(max(ws, 16), dtype=torch.uint8, device=d)
         self._dec = _Rows(self, B)
         i32 = dict(dtype=torch.int32, device=d)
@@ -1262,7 +1266,7 @@ class HybridEngine(EngineCore):
             # bf16: the heads stacked into the M dimension of tensor-core products over the shared key rows
             _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE,
                                            seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, kd, rk, a.scale,
-                                           sink, R.ya.data_ptr(), st))
+                                           sink, R.ya.data_ptr(), self.attn_ws.data_ptr(), self.attn_ws.numel(), st))
         else:
             _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
                                              PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,

@@ -597,7 +597,8 @@ def kernel_table_pametar(eng, s, batch, chunk, timer):
         def attn():
             _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE, *segs[:2],
                                            R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, kd, a.kv_rank, a.scale,
-                                           eng.vec[wa + "mix.sink"].data_ptr(), R.ya.data_ptr(), eng._st))
+                                           eng.vec[wa + "mix.sink"].data_ptr(), R.ya.data_ptr(), eng.attn_ws.data_ptr(),
+                                           eng.attn_ws.numel(), eng._st))
 
         def attn_plain():
             _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, 0, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE,
