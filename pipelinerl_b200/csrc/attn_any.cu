@@ -141,6 +141,13 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
 #pragma unroll
       for (int i = 0; i < VR; ++i) acc[r][i] *= corr;
     }
+    // the tile's weighted values are summed on their own and then added to the running output: over a long sequence the
+    // rounding error grows with the number of tiles, not of keys
+    float tacc[RW][VR];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+      for (int i = 0; i < VR; ++i) tacc[r][i] = 0.f;
     for (int j = 0; j < nk; ++j) {
       float pj[RW];
       bool used = false;
@@ -155,9 +162,13 @@ __global__ void __launch_bounds__(256) attn_any_kernel(const T* __restrict__ q, 
         const int c = lane + 32 * i;
         const float v = c < vdim ? Vs[j * vdim + c] : 0.f;
 #pragma unroll
-        for (int r = 0; r < RW; ++r) acc[r][i] = fmaf(pj[r], v, acc[r][i]);
+        for (int r = 0; r < RW; ++r) tacc[r][i] = fmaf(pj[r], v, tacc[r][i]);
       }
     }
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+      for (int i = 0; i < VR; ++i) acc[r][i] += tacc[r][i];
   }
 #pragma unroll
   for (int r = 0; r < RW; ++r) {

@@ -3,7 +3,7 @@
 // The tcgen05 kernels (gemm_tc.cu, gemm_tn.cu) need bf16 operands and K % 8 == 0.  This kernel takes any M, N, K, any
 // row strides and fp32 or bf16 operands: it is the GEMM of the true-fp32 serving mode and of layers whose sizes the
 // TMA descriptors cannot express (a rank-r bottleneck with r < 8, an odd projection width).  Every output element is
-// accumulated by ONE thread over k = 0..K-1 in ascending order with fmaf, so its value does not depend on M, on the
+// accumulated by ONE thread over k = 0..K-1 in ascending order with fmaf (in steps of sixteen whose sums are added up), so its value does not depend on M, on the
 // position of the row in the batch or on the tile it falls into: a token's logits are bit-identical whether it is
 // computed alone, in a chunk or in a mixed batch.
 #include "prl_common.cuh"
@@ -49,6 +49,13 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const TA* __restrict__ A,
       Ws[lk + j][lr] = (n < N && k < K) ? to_f32(W[(int64_t)n * ldw + k]) : 0.f;
     }
     __syncthreads();
+    // two levels: the step's sixteen products are summed on their own, then added to the total, so the rounding error
+    // grows with sqrt(16) + sqrt(K / 16) instead of sqrt(K) terms; still one thread, one fixed order per element
+    float part[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < kStepK; ++kk) {
       float a[4], w[4];
@@ -59,8 +66,12 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const TA* __restrict__ A,
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
     __syncthreads();
   }
 #pragma unroll
