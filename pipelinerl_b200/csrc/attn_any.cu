@@ -429,13 +429,15 @@ int dispatch_attn(int vr, const void* q, const void* kp, const void* vp, const i
     if (vr <= 1) return PRL_ATTN_DEC(1);
     if (vr <= 2) return PRL_ATTN_DEC(2);
     if (vr <= 4) return PRL_ATTN_DEC(4);
-    return PRL_ATTN_DEC(8);
+    if (vr <= 8) return PRL_ATTN_DEC(8);
+    return PRL_ATTN_DEC(16);
   }
 #undef PRL_ATTN_DEC
   if (vr <= 1) return PRL_ATTN(1);
   if (vr <= 2) return PRL_ATTN(2);
   if (vr <= 4) return PRL_ATTN(4);
-  return PRL_ATTN(8);
+  if (vr <= 8) return PRL_ATTN(8);
+  return PRL_ATTN(16);
 #undef PRL_ATTN
 }
 
@@ -461,8 +463,8 @@ static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, 
   PRL_CHECK_ARG(q && k_pool && v_pool && block_table && seg_start && seg_len && seg_pos0 && seg_slot && out,
                 "prl_attn_any: NULL argument");
   PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && H <= 65535 && G >= 1 && H % G == 0 && dim >= 1 &&
-                dim <= 512 && vdim >= 1 && vdim <= 256 && page_size >= 1 && max_blocks >= 1,
-                "prl_attn_any: bad shape (H=%d G=%d dim=%d vdim=%d; dim <= 512, vdim <= 256)", H, G, dim, vdim);
+                dim <= 1024 && vdim >= 1 && vdim <= 512 && page_size >= 1 && max_blocks >= 1,
+                "prl_attn_any: bad shape (H=%d G=%d dim=%d vdim=%d; dim <= 1024, vdim <= 512)", H, G, dim, vdim);
   PRL_CHECK_ARG(window >= 0 && keep_first >= 0 && softcap >= 0.f, "prl_attn_any: bad mask (window=%d keep_first=%d)", window, keep_first);
   const int vr = (vdim + 31) / 32;
   if (!f32 && g_attn_tensor_cores && max_q >= kMmaMinRows && !sink && ldv == vdim && attn_mma_fits(dim, vdim, q, k_pool, v_pool))

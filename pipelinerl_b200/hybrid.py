@@ -370,8 +370,8 @@ class HybridConfig:
         for i, L in enumerate(self.layers):
             if L.kind == "latent":
                 a = L.latent
-                if a.rot_dim % 2 or a.kv_rank > 256 or a.kv_rank + a.rot_dim > 512 or min(a.heads, a.dim, a.vdim, a.q_rank) < 1:
-                    raise ValueError(f"layer run {i}: bad latent-attention geometry {a} (kv_rank <= 256, even rot_dim)")
+                if a.rot_dim % 2 or a.kv_rank > 512 or a.kv_rank + a.rot_dim > 1024 or min(a.heads, a.dim, a.vdim, a.q_rank) < 1:
+                    raise ValueError(f"layer run {i}: bad latent-attention geometry {a} (kv_rank <= 512, even rot_dim)")
                 if not L.hyper and self.streams != 1:
                     raise ValueError(f"layer run {i}: several streams need the layer's stream weights")
             elif L.kind == "delta":

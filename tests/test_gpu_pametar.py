@@ -32,6 +32,9 @@ def _mechanisms():
         "delta_rule": (pc.model([D()]), {}),
         "delta_one_head_rank_one": (pc.model([D(heads=1, dim=33, rank=1)]), {}),
         "delta_many_small_heads": (pc.model([D(heads=7, dim=4, rank=9)]), {}),
+        "delta_wide_heads": (pc.model([D(heads=1, dim=128, rank=3), D(heads=1, dim=200, rank=2)], width=56), {}),
+        "latent_wide_latent": (pc.model([L(heads=2, dim=8, rot_dim=4, vdim=8, kv_rank=300, q_rank=16)], width=48), {}),
+        "odd_width_six_streams": (pc.model([L(mlp=M()), D(mlp=M(experts=2, top=1, ff=7))], vocab=61, width=50, streams=6), {}),
         "one_stream": (pc.model([L(mlp=M()), D()], streams=1), {}),
         "one_stream_plain_residual": (pc.model([D(mlp=M()), L()], streams=1), dict(hyper=False)),
         "four_streams": (pc.model([L(), D(mlp=M())], streams=4), {}),

@@ -57,7 +57,7 @@ def test_streams_need_their_weights_and_sizes_are_checked():
     bad = pc.model([pc.latent(rot_dim=5)])
     with pytest.raises(ValueError):
         HybridConfig.from_pametar(bad)
-    bad = pc.model([pc.latent(kv_rank=300)])
+    bad = pc.model([pc.latent(kv_rank=600)])
     with pytest.raises(ValueError):
         HybridConfig.from_pametar(bad)
     bad = _config()
