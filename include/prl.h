@@ -740,10 +740,6 @@ int prl_moe_glu(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, cons
                 float limit, float beta, void* out, int32_t f32, prl_stream_t stream);
 
 /* ---- latent attention, delta-rule memory, multi-stream residual (csrc/latent_ops.cu, delta_scan.cu, stream_ops.cu) ---- */
-/* `batch` independent products C_b = A_b W_b^T in one launch; the *_batch strides are in elements */
-int prl_gemm_any_batched(const void* A, int32_t a_is_f32, int64_t lda, int64_t a_batch, const void* W, int32_t w_is_f32,
-                         int64_t ldw, int64_t w_batch, int64_t M, int64_t N, int64_t K, float* C, int64_t ldc,
-                         int64_t c_batch, int32_t batch, prl_stream_t stream);
 /* prl_attn_any_masked with a value row stride (v_pool may alias k_pool: values = leading channels of the key rows) and a
  * per-head sink logit (NULL = none) that joins the softmax denominator only */
 int prl_attn_any_sink(const void* q, const void* k_pool, const void* v_pool, int32_t ldv, int32_t f32,

@@ -330,8 +330,6 @@ _SIGNATURES = {
     "prl_moe_glu": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_float, C.c_float,
                               C.c_void_p, C.c_int32, C.c_void_p]),
     # ---- latent attention, delta-rule memory, multi-stream residual (csrc/latent_ops.cu, delta_scan.cu, stream_ops.cu) ----
-    "prl_gemm_any_batched": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int64, C.c_int64,
-                                       C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "prl_attn_any_sink": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_int32,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                     C.c_int32, C.c_int32, C.c_float, C.c_int32, C.c_int32, C.c_float, C.c_void_p, C.c_int32,

@@ -21,14 +21,11 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(256) gemm_any_kernel(const TA* __restrict__ A, int64_t lda, const TW* __restrict__ W,
                                                        int64_t ldw, int M, int N, int K, float* __restrict__ C,
-                                                       int64_t ldc, int64_t a_batch, int64_t w_batch, int64_t c_batch) {
+                                                       int64_t ldc) {
   pdl_wait();   // launched with the programmatic-serialization attribute like the engine's other step kernels; no early
                 // trigger: letting the next grid become resident early measured +3 ms on a 4096-token prefill and +-0 on decode
   __shared__ float As[kStepK][kTile + 4];
   __shared__ float Ws[kStepK][kTile + 4];
-  A += blockIdx.z * a_batch;      // batched products: member z reads and writes at its own offsets
-  W += blockIdx.z * w_batch;
-  C += blockIdx.z * c_batch;
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * kTile, n0 = blockIdx.x * kTile;
   const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
@@ -88,9 +85,9 @@ __global__ void __launch_bounds__(256) gemm_any_kernel(const TA* __restrict__ A,
 
 template <typename TA, typename TW>
 int launch_any(const void* A, int64_t lda, const void* W, int64_t ldw, int64_t M, int64_t N, int64_t K, float* C,
-               int64_t ldc, cudaStream_t st, int batch = 1, int64_t a_batch = 0, int64_t w_batch = 0, int64_t c_batch = 0) {
-  dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)((M + kTile - 1) / kTile), (unsigned)batch);
-  PRL_CUDA(launch_pdl((gemm_any_kernel<TA, TW>), dim3(grid), dim3(256), (size_t)(0), st, (const TA*)A, lda, (const TW*)W, ldw, (int)M, (int)N, (int)K, C, ldc, a_batch, w_batch, c_batch));
+               int64_t ldc, cudaStream_t st) {
+  dim3 grid((unsigned)((N + kTile - 1) / kTile), (unsigned)((M + kTile - 1) / kTile));
+  PRL_CUDA(launch_pdl((gemm_any_kernel<TA, TW>), dim3(grid), dim3(256), (size_t)(0), st, (const TA*)A, lda, (const TW*)W, ldw, (int)M, (int)N, (int)K, C, ldc));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
@@ -113,18 +110,3 @@ extern "C" int prl_gemm_any(const void* A, int32_t a_is_f32, int64_t lda, const 
   return launch_any<__nv_bfloat16, __nv_bfloat16>(A, lda, W, ldw, M, N, K, C, ldc, st);
 }
 
-// `batch` independent products in one launch: member b uses A + b * a_batch, W + b * w_batch, C + b * c_batch (strides in
-// elements).  Per-head projections that read and write column blocks of shared row buffers are one call.
-extern "C" int prl_gemm_any_batched(const void* A, int32_t a_is_f32, int64_t lda, int64_t a_batch, const void* W,
-                                    int32_t w_is_f32, int64_t ldw, int64_t w_batch, int64_t M, int64_t N, int64_t K, float* C,
-                                    int64_t ldc, int64_t c_batch, int32_t batch, prl_stream_t stream) {
-  PRL_CHECK_ARG(A && W && C, "prl_gemm_any_batched: NULL argument");
-  PRL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && lda >= K && ldw >= K && ldc >= N && M < (1 << 22) && N < (1 << 30) && batch >= 1 &&
-                batch <= 65535, "prl_gemm_any_batched: bad shape (M=%lld N=%lld K=%lld batch=%d)", (long long)M, (long long)N,
-                (long long)K, batch);
-  cudaStream_t st = (cudaStream_t)stream;
-  if (a_is_f32 && w_is_f32) return launch_any<float, float>(A, lda, W, ldw, M, N, K, C, ldc, st, batch, a_batch, w_batch, c_batch);
-  if (a_is_f32) return launch_any<float, __nv_bfloat16>(A, lda, W, ldw, M, N, K, C, ldc, st, batch, a_batch, w_batch, c_batch);
-  if (w_is_f32) return launch_any<__nv_bfloat16, float>(A, lda, W, ldw, M, N, K, C, ldc, st, batch, a_batch, w_batch, c_batch);
-  return launch_any<__nv_bfloat16, __nv_bfloat16>(A, lda, W, ldw, M, N, K, C, ldc, st, batch, a_batch, w_batch, c_batch);
-}

@@ -778,6 +778,7 @@ class HybridEngine(EngineCore):
         self.tc_attn: dict[int, bool] = {}
         self.lin_state, self.lin_decay, self.mlstm_state, self.mlstm_m = {}, {}, {}, {}
         self.lat_pool, self.delta_state = {}, {}
+        self._head_tables: dict = {}
         if cfg.pair_embed is not None:                   # the last token of the sequence's previous portion
             self.prev_token = self.states.add("prev_token", (1,), dtype=torch.int32)
         for i, L in enumerate(cfg.layers):               # one cache / state per layer RUN, also where weights are shared
@@ -1258,8 +1259,7 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_latent_query(R.aux.data_ptr(), hq, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(),
                                         row_pos.data_ptr(), R.yb.data_ptr(), R.q.data_ptr(), f32, st))
         # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers, into the attention query
-        self._mm_heads(R.yb, H * a.dim, a.dim, self.uk_t[L.weights_of].data_ptr(), a.dim, rk * a.dim, n, rk, a.dim,
-                       R.o, H, R.q, H * kd, kd)
+        self._mm_heads(R.yb, a.dim, self.uk_t[L.weights_of].data_ptr(), rk * a.dim, n, rk, R.o, H, R.q, kd)
         pool = self.lat_pool[i].data_ptr()
         sink = vec[w + "mix.sink"].data_ptr() if a.sink else None
         if not self.f32 and not self.force_plain_attn and lib.prl_attn_latent_fits(kd, rk, PAGE_SIZE):
@@ -1272,24 +1272,31 @@ class HybridEngine(EngineCore):
                                              PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
                                              rk, a.scale, 0, 0, 0.0, sink, 1, R.ya.data_ptr(), st))
         # v[h] = W_uv,h o_lat[h], then the output projection over the concatenated heads
-        self._mm_heads(R.ya, H * rk, rk, self.arena.ptr(w + "mix.uv"), rk, a.vdim * rk, n, a.vdim, rk,
-                       R.o, H, R.yb, H * a.vdim, a.vdim)
+        self._mm_heads(R.ya, rk, self.arena.ptr(w + "mix.uv"), a.vdim * rk, n, a.vdim, R.o, H, R.yb, a.vdim)
         k0 = self._mm(R.yb, H * a.vdim, w + "mix.o", W, R.y0, n, split=True)
         return R.y0, k0, (P + 4 * (a.q_rank + kd)) if L.gated else None, ld
 
-    def _mm_heads(self, src, lda, a_step, w_ptr, ldw, w_step, n, N, K, tmp, heads, dst, ld_dst, dst_step) -> None:
-        """dst[:, h*dst_step : +N] (operand type) = src[:, h*a_step : +K] @ W_h[N, K]^T for every head h (W_h = w_ptr +
-        h * w_step elements).  bf16 prompt batches: one tcgen05 GEMM per head writing bf16 in place; otherwise one batched
-        CUDA-core launch into the fp32 buffer `tmp` and a cast."""
+    def _head_table(self, n: int, heads: int):
+        """Tile table of the grouped GEMM (csrc/moe_ops.cu) for per-head products over token-major buffers: the rows
+        (token t, head h) = t * heads + h of a [n][heads][.] buffer, grouped by head.  Cached per (n, heads); built on
+        the first use, which for the decode step is its eager run before the graph capture."""
+        key = (n, heads)
+        if key not in self._head_tables:
+            i32 = dict(dtype=torch.int32, device=self.dev)
+            perm = (torch.arange(n, dtype=torch.int32).view(1, n) * heads + torch.arange(heads, dtype=torch.int32).view(heads, 1)).reshape(-1)
+            tiles = [(h, h * n + r0, min(64, n - r0)) for h in range(heads) for r0 in range(0, n, 64)]
+            self._head_tables[key] = (perm.to(self.dev), torch.tensor([len(tiles), 0, 0, 0], **i32),
+                                      torch.tensor(tiles, **i32).reshape(-1), len(tiles))
+        return self._head_tables[key]
+
+    def _mm_heads(self, src, K, w_ptr, w_step, n, N, tmp, heads, dst, dst_step) -> None:
+        """dst[t][h][:N] (operand type, rows dst_step apart) = src[t][h][:K] @ W_h[N, K]^T for every token t and head h
+        (W_h = w_ptr + h * w_step elements, rows K apart): ONE grouped GEMM over the heads (tensor cores for bf16), the
+        routed feed-forward's kernel with the head in the expert's place, into the fp32 buffer `tmp`, and a cast."""
         lib, st, f32 = self.lib, self._st, int(self.f32)
-        if (not self.f32 and not self.force_plain_gemm and n > 128 and K >= 16 and K % 8 == 0 and lda % 8 == 0 and ldw % 8 == 0
-                and a_step % 8 == 0 and w_step % 8 == 0 and ld_dst % 8 == 0 and dst_step % 8 == 0):
-            for h in range(heads):
-                _lib.check(lib.prl_gemm_tn(src.data_ptr() + 2 * h * a_step, lda, w_ptr + 2 * h * w_step, ldw, n, N, K,
-                                           dst.data_ptr() + 2 * h * dst_step, ld_dst, 0, 0, None, None, 0, 1.0, st))
-            return
-        _lib.check(lib.prl_gemm_any_batched(src.data_ptr(), f32, lda, a_step, w_ptr, f32, ldw, w_step, n, N, K,
-                                            tmp.data_ptr(), heads * N, N, heads, st))
+        perm, meta, tiles, n_tiles = self._head_table(n, heads)
+        _lib.check(lib.prl_moe_gemm(src.data_ptr(), f32, K, n * heads, w_ptr, f32, w_step, K, perm.data_ptr(), meta.data_ptr(),
+                                    tiles.data_ptr(), n_tiles, N, K, tmp.data_ptr(), N, 1, st))
         _lib.check(lib.prl_store_groups(tmp.data_ptr(), heads * N, n, heads, N, dst.data_ptr(), dst_step, f32, st))
 
     def _delta_mixer(self, R, n, i, L, w, segs, max_q=0):
