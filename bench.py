@@ -63,7 +63,7 @@ def parse():
                          "(tools/hybrid_bench.py); belelorn: the same for the Belelorn design (mLSTM, windowed attention "
                          "beside lightning attention, routed feed-forwards) beside the Povurax hybrid and Qwen2; pametar: the "
                          "Pametar design (latent attention, delta-rule memory, residual streams) beside Belelorn and Qwen2; "
-                         "the default workload and its JSON contract are unchanged")
+                         "the default workload and its JSON line are unchanged")
     ap.add_argument("--sizes", default="w2048,w4096", help="--arch hybrid: model sizes to compare")
     return ap.parse_args()
 

@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
   const int n_tiles = pos_tok / kKeys + 1;
   Acc<NV> acc;
   acc.init();
-  for (int t = z * kSplitWarps + warp; t < n_tiles; t += kSplitWarps * splits) {     // CTA z of `splits` takes every splits-th round
+  for (int t = z * kSplitWarps + warp; t < n_tiles; t += kSplitWarps * splits) {     // CTA z of `splits` takes every splits-th turn
     __syncwarp();
     stage_keys(Ks, ld, pool, bt, page_size, kd, t * kKeys, pos_tok, lane, 32);
     cp_commit();

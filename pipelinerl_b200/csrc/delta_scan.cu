@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(kThreads) delta_scan_kernel(DeltaArgs a) {
   for (int c = 0; c < n_chunks; ++c) {
     const int t0 = c * TT, nt = min(TT, len - t0);
     const float* buf = sm + (c & 1) * buf_floats;
-    issue(c + 1);                                 // its buffer was walked in the round before
+    issue(c + 1);                                 // its buffer was walked one chunk ago
     cp_wait<1>();
     __syncthreads();
     // Only u^T S (its shuffle tree) sits on the chain from token to token: the lanes' shares of S^T r go to shared
@@ -196,8 +196,8 @@ __global__ void __launch_bounds__(kThreads) delta_scan_kernel(DeltaArgs a) {
         a.out[(row0 + t0 + t) * a.ld_out + head * dv + col0 + ch] = o;
       }
     }
-    // the next round's copies overwrite the buffer walked in this one, and its walk the partial sums: both wait for the
-    // barrier behind the next cp_wait
+    // the next chunk's copies overwrite the buffer walked here, and its walk the partial sums: both come behind the
+    // barrier that follows the next cp_wait
   }
   if (col_on) {
 #pragma unroll

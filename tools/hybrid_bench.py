@@ -78,7 +78,7 @@ def pametar_config(s):
     routed = dict(kind="moe", router=dict(experts=16, top=4, scale=1.0), expert=dict(ff=ff // 4))
     layers = [dict(att if i % 2 == 0 else mem, mlp=routed) for i in range(s["layers"] - 2)]
     return dict(architecture="Pametar", vocab=s["vocab"], width=W, norm=dict(eps=1e-5), streams=4,
-                embedding=dict(scale=1.0, bigram=dict(buckets=65521, mul_prev=31, mul_cur=7)), layers=layers,
+                embedding=dict(scale=1.0, bigram=dict(buckets=65521, mul_prev=131, mul_cur=17)), layers=layers,
                 loop=dict(start=0, stop=2, times=2))
 
 
