@@ -1,6 +1,5 @@
 """Small Pametar configurations and helpers for the tests (random weights, sizes chosen to be awkward)."""
 import copy
-import math
 
 import torch
 
