@@ -727,10 +727,11 @@ int prl_mlstm_out(const float* o_aug, int32_t n, int32_t H, int32_t dv, const fl
 /* routed feed-forward: top-k routing + grouping of the (choice, row) pairs by expert; grouped GEMM over the tile table;
  * gated activation with the pair's weight folded into gate and up */
 int64_t prl_moe_max_tiles(int64_t pairs, int32_t experts);
-int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t experts, int32_t top, int32_t softmax_weights,
+int prl_moe_route(const float* logits, int64_t ld, const float* bias /* [experts] added to the logits, or NULL */, int32_t n,
+                  int32_t experts, int32_t top, int32_t softmax_weights,
                   int32_t* sel, float* wsel, int32_t* perm, int32_t* meta, int32_t* tiles, prl_stream_t stream);
 /* router product (fp32 sums in a fixed order), choice and grouping without the logits going through memory */
-int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, int32_t n, int32_t W, int32_t experts,
+int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, const float* bias, int32_t n, int32_t W, int32_t experts,
                    int32_t top, int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm, int32_t* meta,
                    int32_t* tiles, prl_stream_t stream);
 int prl_moe_gemm(const void* A, int32_t a_is_f32, int64_t lda, int32_t a_mod, const void* W, int32_t w_is_f32,
@@ -760,16 +761,17 @@ int prl_attn_latent(const void* q, const void* pool, const int32_t* block_table,
                     int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank, float scale, const float* sink,
                     void* out, void* ws, size_t ws_bytes, prl_stream_t stream);
 /* query latent cq = rmsnorm(P[off_q : off_q + q_rank]) * q_gain (operand type) and the latent cache row
- * [rmsnorm(P[off_kv : +rank]) * kv_gain | rotate_half(P[off_kv + rank : +rot], pos)] -> pool[page][page_size][rank + rot] */
+ * [rmsnorm(P[off_kv : +rank]) * kv_gain | rotate(P[off_kv + rank : +rot], pos)] -> pool[page][page_size][rank + rot];
+ * rotation pairs (i, i + rot/2), or (2i, 2i + 1) when `interleaved`; q_rank = 0: no query latent (q_gain, cq_out unused) */
 int prl_latent_prep(const float* P, int64_t ldp, int32_t off_q, int32_t q_rank, int32_t off_kv, int32_t rank, int32_t rot,
                     const double* freq, const float* q_gain, const float* kv_gain, float eps, const int32_t* row_pos,
                     const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks, int32_t page_size, int32_t n,
-                    void* cq_out, void* pool, int32_t f32, prl_stream_t stream);
-/* per head [dim | rot] of Q: the unrotated parts -> q_plain [n][H*dim], the rotated part (rotate-half at the row's
- * position) -> q_att[n][H][rank + rot] behind its first `rank` channels */
+                    int32_t interleaved, void* cq_out, void* pool, int32_t f32, prl_stream_t stream);
+/* per head [dim | rot] of Q: the unrotated parts -> q_plain [n][H*dim], the rotated part (turned at the row's
+ * position, pairs as above) -> q_att[n][H][rank + rot] behind its first `rank` channels */
 int prl_latent_query(const float* Q, int64_t ldq, int32_t n, int32_t H, int32_t dim, int32_t rot, int32_t rank,
-                     const double* freq, const int32_t* row_pos, void* q_plain, void* q_att, int32_t f32,
-                     prl_stream_t stream);
+                     const double* freq, const int32_t* row_pos, int32_t interleaved, void* q_plain, void* q_att,
+                     int32_t f32, prl_stream_t stream);
 /* out[r][g][c] = T(src[r][g*C + c]), rows of out ld_out apart per group (G = 1: a cast of fp32 rows to the operand type) */
 int prl_store_groups(const float* src, int64_t lds, int32_t n, int32_t G, int32_t C, void* out, int64_t ld_out, int32_t f32,
                      prl_stream_t stream);
@@ -804,6 +806,40 @@ int prl_streams_close(const float* y, int64_t ldy, int32_t n_split, int64_t spli
  * projection).  prl_moe_route / prl_moe_router take softmax_weights = 2 for a softmax over ALL experts */
 int prl_moe_glu_out(const float* gate_up, int64_t ld, int64_t pairs, int32_t F, const int32_t* perm, const float* wsel,
                     float wscale, void* out, int32_t f32, prl_stream_t stream);
+
+/* ---- norm after the sum, attention front end with per-head norms and blended values, attention without a softmax,
+ *      the gated delta rule (csrc/hybrid_ops.cu, attn_sigmoid.cu, delta_scan.cu) ---- */
+/* v = alpha x + s0 sum(y0 slices) + s1 sum(y1 slices) + bias;  x <- v / sqrt(mean(v^2) + eps) * gain;  xa = T(x) */
+int prl_postln_close(const float* y0, int64_t ld0, float s0, int32_t n_split0, const float* y1, int64_t ld1, float s1,
+                     int32_t n_split1, const float* bias, float alpha, const float* gain, float eps, int32_t n, int32_t W,
+                     float* x, void* xa, int32_t f32, prl_stream_t stream);
+/* q, k: + bias, RMS norm per head (qk_norm) with gain[(head * dim + c) % gain_period], rotate-half on the first `rot`
+ * channels with cos and sin times `mag`; v: + bias, unit RMS per head (v_norm), v_blend 1: also stored to v_first
+ * [n][G * vdim] fp32, 2: v <- (1 - *v_lambda) v + *v_lambda v_first; q -> q_out [n][H][dim], k and v -> the paged pools */
+int prl_attn_front(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n, int32_t H, int32_t G,
+                   int32_t dim, int32_t vdim, const float* q_bias, const float* k_bias, const float* v_bias, int32_t qk_norm,
+                   const float* q_gain, const float* k_gain, int32_t gain_period, float eps, int32_t rot, const double* freq,
+                   float mag, int32_t v_norm, int32_t v_blend, const float* v_lambda, float* v_first, const int32_t* row_pos,
+                   const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks, int32_t page_size, void* q_out,
+                   void* k_pool, void* v_pool, int32_t f32, prl_stream_t stream);
+/* out[r][h * dv + j] = T(o[r][h * dv + j] * sigmoid(g[r][h])) */
+int prl_gate_heads(const void* o, int32_t o_f32, int64_t ldo, const float* g, int64_t ldg, int32_t n, int32_t H, int32_t dv,
+                   void* out, int32_t f32, prl_stream_t stream);
+/* causal attention whose weights are sigmoid(cap(q . k * scale * temp(pos)) + head_bias[h]), not normalised over the keys,
+ * mixed over the heads by talk [H][H] (NULL: none); temp(p) = 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) */
+int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
+                     int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
+                     const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H, int32_t G,
+                     int32_t dim, int32_t vdim, float scale, float softcap, float temp_coef, float temp_every,
+                     const float* head_bias, const float* talk, int32_t out_is_t, void* out, prl_stream_t stream);
+/* S <- g S; d = beta (v - S^T k); S <- S + k d^T; o = S^T q with unit q (times dk^(-1/2)) and k, beta = sigmoid(Z[off_b + h]),
+ * g = exp(-exp(A_log[h]) softplus(Z[off_a + h] + dt_bias[h])); `kh` q / k heads serve `heads` value heads; scratch
+ * [n_rows][5 * heads * dk] fp32; state [slot][head][dv][dk] fp32 */
+int prl_gated_delta_scan(const float* C, int64_t ldc, int32_t off_q, int32_t off_k, int32_t off_v, const float* Z, int64_t ldz,
+                         int32_t off_b, int32_t off_a, const float* A_log, const float* dt_bias, float unit_eps, int32_t heads,
+                         int32_t kh, int32_t dk, int32_t dv, int32_t n_rows, float* scratch, const int32_t* seg_start,
+                         const int32_t* seg_len, const int32_t* seg_slot, int32_t n_seg, int32_t max_len, float* state,
+                         float* out, int64_t ld_out, prl_stream_t stream);
 
 #ifdef __cplusplus
 }

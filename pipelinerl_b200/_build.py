@@ -73,7 +73,7 @@ def _compile_one(src: Path, verbose: bool) -> tuple[Path, bool]:
 # what the sampler engines (engine.py, hybrid.py) call: enough for a command-line tool that only serves a model
 SAMPLER_SOURCES = ("prl_core.cu", "decode_ops.cu", "gemm_tc.cu", "gemm_tn.cu", "gemm_any.cu", "paged_attn.cu", "attn_tc.cu",
                    "attn_any.cu", "attn_mma.cu", "hybrid_ops.cu", "lin_scan.cu", "moe_ops.cu", "latent_ops.cu", "attn_latent.cu", "delta_scan.cu",
-                   "stream_ops.cu")
+                   "stream_ops.cu", "attn_sigmoid.cu")
 LINKED_LIST = LIB_DIR / "libprl.sources"
 
 

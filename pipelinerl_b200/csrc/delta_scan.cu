@@ -18,6 +18,14 @@
 // bit-identical across schedules.
 //
 // State: [slot][head][dv][dk] fp32 (a column's key channels contiguous), read at a segment's start, written at its end.
+//
+// A second front end, the GATED delta rule with one decay g and one step size beta per head and token,
+//
+//     S <- g S;   d = beta (v - S^T k);   S <- S + k d^T;   o = S^T q          (q, k of unit length, q times dk^(-1/2))
+//
+// is the same walk: S_t = g S_(t-1) - (beta g k)(k^T S_(t-1)) + (beta k) v^T, i.e. u = k, a u = beta g k, w = g on
+// every channel, and beta k in the key's place.  gated_delta_prep forms these vectors per VALUE head (several value
+// heads may share one q / k head) from the convolved q, k and the gate logits.
 #include "prl_common.cuh"
 #include <math.h>
 
@@ -47,6 +55,8 @@ struct DeltaArgs {
   int64_t ldw;
   const float* u;          // unit keys [row][heads * dk]
   int64_t ldu;
+  const float* V;          // values [row][heads * dv] at V + row * ldv (the caller folds the column offset in)
+  int64_t ldv;
   int heads, dk, dv, chunk, vec4;
   const int32_t* seg_start;
   const int32_t* seg_len;
@@ -54,6 +64,7 @@ struct DeltaArgs {
   float* state;
   float* out;
   int64_t ld_out;
+  int n_seg;
 };
 
 // One warp per (token, head): u = k / sqrt(sum k^2 + eps) -> u_out; P[off_a] <- sigmoid(P[off_a] + a_bias) * u;
@@ -76,6 +87,44 @@ __global__ void delta_prep_kernel(float* __restrict__ P, int64_t ldp, int off_k,
       u_out[row * ldu + hoff + i] = u;
       p[off_a + hoff + i] = sigmoid_f(p[off_a + hoff + i] + a_bias[hoff + i]) * u;
       zw[row * ldw + hoff + i] = expf(-decay_scale * sigmoid_f(zw[row * ldw + hoff + i] + w_bias[hoff + i]));
+    }
+  }
+}
+
+// One warp per (token, value head).  C holds the convolved, activated q | k (kh heads of dk each) of the row; Z the
+// logits of beta and of the decay.  D [row][5 * heads * dk] receives u | a u | w | k | r, each [heads][dk]:
+//   u = k / sqrt(sum k^2 + unit_eps),  r = q / sqrt(sum q^2 + unit_eps) * dk^(-1/2),
+//   beta = sigmoid(Z[off_b + h]),  g = exp(-exp(A_log[h]) * softplus(Z[off_a + h] + dt_bias[h])).
+__global__ void gated_delta_prep_kernel(const float* __restrict__ C, int64_t ldc, int off_q, int off_k,
+                                        const float* __restrict__ Z, int64_t ldz, int off_b, int off_a,
+                                        const float* __restrict__ A_log, const float* __restrict__ dt_bias, float unit_eps,
+                                        int heads, int kh, int dk, float* __restrict__ D) {
+  pdl_wait();
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int64_t ldd = (int64_t)5 * heads * dk, hd = (int64_t)heads * dk;
+  const float q_scale = 1.f / sqrtf((float)dk);
+  for (int head = threadIdx.x >> 5; head < heads; head += blockDim.x >> 5) {
+    const int src_head = head / (heads / kh);
+    const float* q = C + row * ldc + off_q + src_head * dk;
+    const float* k = C + row * ldc + off_k + src_head * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int i = lane; i < dk; i += 32) { sq = fmaf(q[i], q[i], sq); sk = fmaf(k[i], k[i], sk); }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float inv_q = q_scale / sqrtf(sq + unit_eps), inv_k = 1.f / sqrtf(sk + unit_eps);
+    const float beta = sigmoid_f(Z[row * ldz + off_b + head]);
+    const float z = Z[row * ldz + off_a + head] + dt_bias[head];
+    const float sp = z > 20.f ? z : log1pf(expf(z));
+    const float g = expf(-expf(A_log[head]) * sp);
+    float* d = D + row * ldd + head * dk;
+    for (int i = lane; i < dk; i += 32) {
+      const float u = k[i] * inv_k;
+      d[i] = u;
+      d[hd + i] = beta * g * u;
+      d[2 * hd + i] = g;
+      d[3 * hd + i] = beta * u;
+      d[4 * hd + i] = q[i] * inv_q;
     }
   }
 }
@@ -123,7 +172,7 @@ __global__ void __launch_bounds__(kThreads) delta_scan_kernel(DeltaArgs a) {
       }
       for (int i = tid; i < nt * kCols; i += kThreads) {
         const int t = i / kCols, ch = i - t * kCols;
-        if (col0 + ch < dv) cp4(buf + t * tok_floats + 5 * dkp + ch, a.P + (row0 + t0 + t) * a.ldp + a.off_v + head * dv + col0 + ch);
+        if (col0 + ch < dv) cp4(buf + t * tok_floats + 5 * dkp + ch, a.V + (row0 + t0 + t) * a.ldv + head * dv + col0 + ch);
       }
     }
     cp_commit();
@@ -215,6 +264,37 @@ __global__ void __launch_bounds__(kThreads) delta_scan_kernel(DeltaArgs a) {
 
 using namespace prl;
 
+// Launch of the walking kernel for prepared vectors (shared by the front ends below).
+static int launch_delta_walk(DeltaArgs a, int max_len, cudaStream_t s) {
+  const int dk = a.dk, dv = a.dv;
+  // (key channels per lane, lanes per value column): four channels per lane up to dk = 128, so that a warp's instruction
+  // stream per token is short; the shuffle tree grows with the lanes
+  const int lanes = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 64 ? 16 : 32));
+  const int R = dk <= 128 ? 4 : 8;
+  const int dkp = R * lanes, cols = (32 / lanes) * kWarps;
+  a.chunk = 16;                                       // tokens per staged chunk, two chunks in shared memory
+  if (max_len >= 1 && max_len < a.chunk) a.chunk = max_len;     // a decode step stages one token
+  // 16-byte copies when every source address is a multiple of 16 bytes
+  a.vec4 = dk % 4 == 0 && a.ldp % 4 == 0 && a.ldw % 4 == 0 && a.ldu % 4 == 0 && a.off_r % 4 == 0 && a.off_k % 4 == 0 && a.off_a % 4 == 0 &&
+           ((uintptr_t)a.P & 15) == 0 && ((uintptr_t)a.w & 15) == 0 && ((uintptr_t)a.u & 15) == 0;
+  const size_t smem = ((size_t)2 * a.chunk * (5 * dkp + cols) + (size_t)a.chunk * cols * lanes) * sizeof(float);   // <= 166 KB
+  dim3 grid((dv + cols - 1) / cols, a.heads, a.n_seg);
+  static SmemAttr attr[5] = {};
+#define PRL_DELTA(RR, LL, I)                                                                  \
+  do {                                                                                        \
+    PRL_CUDA(ensure_smem((delta_scan_kernel<RR, LL>), (int)smem, attr[I]));                   \
+    PRL_CUDA(launch_pdl((delta_scan_kernel<RR, LL>), grid, dim3(kThreads), smem, s, a));      \
+  } while (0)
+  if (R == 8) PRL_DELTA(8, 32, 4);
+  else if (lanes == 4) PRL_DELTA(4, 4, 0);
+  else if (lanes == 8) PRL_DELTA(4, 8, 1);
+  else if (lanes == 16) PRL_DELTA(4, 16, 2);
+  else PRL_DELTA(4, 32, 3);
+#undef PRL_DELTA
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
 extern "C" int64_t prl_delta_state_floats(int32_t heads, int32_t dk, int32_t dv) { return (int64_t)heads * dk * dv; }
 
 extern "C" int prl_delta_scan(float* P, int64_t ldp, int32_t off_r, int32_t off_k, int32_t off_v, int32_t off_a, float* zw,
@@ -232,32 +312,33 @@ extern "C" int prl_delta_scan(float* P, int64_t ldp, int32_t off_r, int32_t off_
   PRL_CUDA(launch_pdl(delta_prep_kernel, dim3(n_rows), dim3(32 * pw), (size_t)0, s, P, ldp, off_k, off_a, zw, ldw, w_bias, a_bias,
                       decay_scale, unit_eps, heads, dk, unit_keys, ldu));
   PRL_LAUNCH_CHECK();
-  DeltaArgs a{P, ldp, off_r, off_k, off_v, off_a, zw, ldw, unit_keys, ldu, heads, dk, dv, 0, 0,
-              seg_start, seg_len, seg_slot, state, out, ld_out};
-  // (key channels per lane, lanes per value column): four channels per lane up to dk = 128, so that a warp's instruction
-  // stream per token is short; the shuffle tree grows with the lanes
-  const int lanes = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 64 ? 16 : 32));
-  const int R = dk <= 128 ? 4 : 8;
-  const int dkp = R * lanes, cols = (32 / lanes) * kWarps;
-  a.chunk = 16;                                       // tokens per staged chunk, two chunks in shared memory
-  if (max_len >= 1 && max_len < a.chunk) a.chunk = max_len;     // a decode step stages one token
-  // 16-byte copies when every source address is a multiple of 16 bytes
-  a.vec4 = dk % 4 == 0 && ldp % 4 == 0 && ldw % 4 == 0 && off_r % 4 == 0 && off_k % 4 == 0 && off_a % 4 == 0 &&
-           ((uintptr_t)P & 15) == 0 && ((uintptr_t)zw & 15) == 0 && ((uintptr_t)unit_keys & 15) == 0;
-  const size_t smem = ((size_t)2 * a.chunk * (5 * dkp + cols) + (size_t)a.chunk * cols * lanes) * sizeof(float);   // <= 166 KB
-  dim3 grid((dv + cols - 1) / cols, heads, n_seg);
-  static SmemAttr attr[5] = {};
-#define PRL_DELTA(RR, LL, I)                                                                  \
-  do {                                                                                        \
-    PRL_CUDA(ensure_smem((delta_scan_kernel<RR, LL>), (int)smem, attr[I]));                   \
-    PRL_CUDA(launch_pdl((delta_scan_kernel<RR, LL>), grid, dim3(kThreads), smem, s, a));      \
-  } while (0)
-  if (R == 8) PRL_DELTA(8, 32, 4);
-  else if (lanes == 4) PRL_DELTA(4, 4, 0);
-  else if (lanes == 8) PRL_DELTA(4, 8, 1);
-  else if (lanes == 16) PRL_DELTA(4, 16, 2);
-  else PRL_DELTA(4, 32, 3);
-#undef PRL_DELTA
+  DeltaArgs a{P, ldp, off_r, off_k, off_v, off_a, zw, ldw, unit_keys, ldu, P + off_v, ldp, heads, dk, dv, 0, 0,
+              seg_start, seg_len, seg_slot, state, out, ld_out, n_seg};
+  return launch_delta_walk(a, max_len, s);
+}
+
+// The gated delta rule over ragged segments.  C [n_rows][ldc]: the convolved and activated q (off_q), k (off_k), both
+// kh heads of dk, and v (off_v, `heads` heads of dv); Z [n_rows][ldz]: the logits of beta (off_b) and of the decay
+// (off_a), one per value head; scratch [n_rows][5 * heads * dk] fp32; state as prl_delta_state_floats(heads, dk, dv).
+extern "C" int prl_gated_delta_scan(const float* C, int64_t ldc, int32_t off_q, int32_t off_k, int32_t off_v, const float* Z,
+                                    int64_t ldz, int32_t off_b, int32_t off_a, const float* A_log, const float* dt_bias,
+                                    float unit_eps, int32_t heads, int32_t kh, int32_t dk, int32_t dv, int32_t n_rows,
+                                    float* scratch, const int32_t* seg_start, const int32_t* seg_len,
+                                    const int32_t* seg_slot, int32_t n_seg, int32_t max_len, float* state, float* out,
+                                    int64_t ld_out, prl_stream_t st) {
+  PRL_CHECK_ARG(C && Z && A_log && dt_bias && scratch && seg_start && seg_len && seg_slot && state && out,
+                "prl_gated_delta_scan: NULL argument");
+  PRL_CHECK_ARG(heads >= 1 && heads <= 65535 && kh >= 1 && heads % kh == 0 && dk >= 1 && dk <= 256 && dv >= 1 && n_seg >= 1 &&
+                n_seg <= 65535 && n_rows >= 1 && ld_out >= (int64_t)heads * dv,
+                "prl_gated_delta_scan: bad shape (heads=%d q/k heads=%d dk=%d dv=%d; dk <= 256)", heads, kh, dk, dv);
+  cudaStream_t s = (cudaStream_t)st;
+  const int pw = heads < 8 ? heads : 8;
+  PRL_CUDA(launch_pdl(gated_delta_prep_kernel, dim3(n_rows), dim3(32 * pw), (size_t)0, s, C, ldc, off_q, off_k, Z, ldz, off_b,
+                      off_a, A_log, dt_bias, unit_eps, heads, kh, dk, scratch));
   PRL_LAUNCH_CHECK();
-  return PRL_OK;
+  const int hd = heads * dk;
+  const int64_t ldd = (int64_t)5 * hd;
+  DeltaArgs a{scratch, ldd, 4 * hd, 3 * hd, 0, hd, scratch + 2 * hd, ldd, scratch, ldd, C + off_v, ldc, heads, dk, dv, 0, 0,
+              seg_start, seg_len, seg_slot, state, out, ld_out, n_seg};
+  return launch_delta_walk(a, max_len, s);
 }

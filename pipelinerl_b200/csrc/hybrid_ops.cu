@@ -560,6 +560,148 @@ __global__ void mlstm_out_kernel(const float* __restrict__ o_aug, int H, int dv,
   }
 }
 
+// Norm AFTER the sum ("post-LN" with a weighted skip):  v = alpha * x + s0 * y0 + s1 * y1 + bias;
+// x <- v / sqrt(mean(v^2) + eps) * gain;  xa = T(x).  y0 / y1 may be split-K slices of a projection or the choices of a
+// routed feed-forward ([slices][n][ld]), summed here in slice order; y1 and bias may be NULL.
+template <typename T>
+__global__ void postln_close_kernel(const float* __restrict__ y0, int64_t ld0, float s0, int ns0, int64_t stride0,
+                                    const float* __restrict__ y1, int64_t ld1, float s1, int ns1, int64_t stride1,
+                                    const float* __restrict__ bias, float alpha, const float* __restrict__ gain, float eps,
+                                    int W, int keep, float* __restrict__ x, T* __restrict__ xa) {
+  pdl_wait();
+  extern __shared__ float vbuf[];    // [W] the row's sum between the two passes (empty: recomputed)
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  auto value = [&](int c) {
+    float a = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < ns0; ++k) a += y0[k * stride0 + (int64_t)r * ld0 + c];
+    float y = s0 * a;
+    if (y1) {
+      float b = 0.f;
+#pragma unroll 4
+      for (int k = 0; k < ns1; ++k) b += y1[k * stride1 + (int64_t)r * ld1 + c];
+      y += s1 * b;
+    }
+    if (bias) y += bias[c];
+    return fmaf(alpha, x[(int64_t)r * W + c], y);
+  };
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = value(c);
+    if (keep) vbuf[c] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);     // its barriers also order every thread's reads of x before the writes below
+  const float inv = 1.f / sqrtf(ss / (float)W + eps);
+  // without the kept copy the second pass reads x again: a thread reads a column before it writes it, and owns it
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = (keep ? vbuf[c] : value(c)) * inv * gain[c];
+    x[(int64_t)r * W + c] = v;
+    stf(xa, (int64_t)r * W + c, v);
+  }
+}
+
+// Attention front end with biases, per-head norms, "rotate half" rotary and normed, blended values.  Per row:
+//   q, k: + bias (NULL: none); each head divided by its root mean square over `dim` and multiplied by a gain indexed
+//         (head * dim + channel) % gain_period (gain NULL: none; qk_norm == 0: no norm at all);
+//         the first `rot` channels of each head turned: channel i < rot / 2 pairs with channel i + rot / 2, the pair
+//         (u, v) becomes mag * (u cos a - v sin a, v cos a + u sin a), a = pos * freq[i] (double);
+//   v:    + bias; v_norm: each head divided by its root mean square over `vdim` (no gain); then
+//         v_blend == 1: the row's values are also written to v_first [n][G * vdim] (fp32) for later layers,
+//         v_blend == 2: v <- (1 - lambda) v + lambda v_first[row], lambda = *v_lambda.
+// q goes to the query buffer [n][H][dim], k and v into the paged cache.  One warp per head.
+template <typename T>
+__global__ void attn_front_kernel(const float* __restrict__ P, int64_t ldp, int off_q, int off_k, int off_v, int H, int G,
+                                  int dim, int vdim, const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                  const float* __restrict__ v_bias, int qk_norm, const float* __restrict__ q_gain,
+                                  const float* __restrict__ k_gain, int gain_period, float eps, int rot,
+                                  const double* __restrict__ freq, float mag, int v_norm, int v_blend,
+                                  const float* __restrict__ v_lambda, float* __restrict__ v_first,
+                                  const int32_t* __restrict__ row_pos, const int32_t* __restrict__ row_slot,
+                                  const int32_t* __restrict__ block_table, int max_blocks, int page_size,
+                                  T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool) {
+  pdl_wait();
+  extern __shared__ float trig[];    // [rot / 2] cos | [rot / 2] sin of the row's angles, times mag
+  const int r = blockIdx.x;
+  const int slot = row_slot[r];
+  if (slot < 0) return;
+  const int pos = row_pos[r];
+  const int half = rot / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sn, cs;
+    sincos((double)pos * freq[i], &sn, &cs);
+    trig[i] = (float)cs * mag;
+    trig[half + i] = (float)sn * mag;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const int page = block_table[(int64_t)slot * max_blocks + pos / page_size], within = pos % page_size;
+  for (int hh = warp; hh < H + 2 * G; hh += nw) {
+    if (hh < H + G) {
+      const bool is_q = hh < H;
+      const int head = is_q ? hh : hh - H;
+      const float* src = P + (int64_t)r * ldp + (is_q ? off_q : off_k) + head * dim;
+      const float* bias = is_q ? q_bias : k_bias;
+      const float* gain = is_q ? q_gain : k_gain;
+      float inv = 1.f;
+      if (qk_norm) {
+        float ss = 0.f;
+        for (int j = lane; j < dim; j += 32) {
+          const float v = src[j] + (bias ? bias[head * dim + j] : 0.f);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / (float)dim + eps);
+      }
+      auto val = [&](int j) {
+        const float raw = src[j] + (bias ? bias[head * dim + j] : 0.f);
+        return raw * inv * (gain ? gain[(head * dim + j) % gain_period] : 1.f);
+      };
+      T* dst = is_q ? q_out + ((int64_t)r * H + head) * dim
+                    : k_pool + (((int64_t)page * G + head) * page_size + within) * dim;
+      for (int i = lane; i < half; i += 32) {
+        const float u = val(i), v = val(i + half), cs = trig[i], sn = trig[half + i];
+        stf(dst, i, u * cs - v * sn);
+        stf(dst, i + half, v * cs + u * sn);
+      }
+      for (int j = 2 * half + lane; j < dim; j += 32) stf(dst, j, val(j));
+    } else {
+      const int head = hh - H - G;
+      const float* src = P + (int64_t)r * ldp + off_v + head * vdim;
+      float inv = 1.f;
+      if (v_norm) {
+        float ss = 0.f;
+        for (int j = lane; j < vdim; j += 32) {
+          const float v = src[j] + (v_bias ? v_bias[head * vdim + j] : 0.f);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / (float)vdim + eps);
+      }
+      const float lam = v_blend == 2 ? *v_lambda : 0.f;
+      float* vf = v_first ? v_first + ((int64_t)r * G + head) * vdim : nullptr;
+      T* dst = v_pool + (((int64_t)page * G + head) * page_size + within) * vdim;
+      for (int j = lane; j < vdim; j += 32) {
+        float v = (src[j] + (v_bias ? v_bias[head * vdim + j] : 0.f)) * inv;
+        if (v_blend == 1) vf[j] = v;
+        else if (v_blend == 2) v = (1.f - lam) * v + lam * vf[j];
+        stf(dst, j, v);
+      }
+    }
+  }
+}
+
+// out[r][h * dv + j] = T(o[r][h * dv + j] * sigmoid(g[r][h])): one gate per head on an attention output
+template <typename T, typename TO>
+__global__ void gate_heads_kernel(const TO* __restrict__ o, int64_t ldo, const float* __restrict__ g, int64_t ldg, int H,
+                                  int dv, T* __restrict__ out) {
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < H * dv; e += gridDim.y * blockDim.x)
+    stf(out, r * H * dv + e, ldf(o, r * ldo + e) * sigmoid_f(g[r * ldg + e / dv]));
+}
+
 inline int row_threads(int width) {
   int t = ((width + 31) / 32) * 32;
   return t < 32 ? 32 : (t > 256 ? 256 : t);
@@ -795,6 +937,58 @@ extern "C" int prl_mlstm_out(const float* o_aug, int32_t n, int32_t H, int32_t d
   const int th = row_threads(dv);
   if (f32) PRL_CUDA(launch_pdl(mlstm_out_kernel<float>, grid, dim3(th), (size_t)0, (cudaStream_t)st, o_aug, H, dv, minv, den_eps, g, ldg, gain, eps, (float*)out));
   else PRL_CUDA(launch_pdl(mlstm_out_kernel<bf16>, grid, dim3(th), (size_t)0, (cudaStream_t)st, o_aug, H, dv, minv, den_eps, g, ldg, gain, eps, (bf16*)out));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_postln_close(const float* y0, int64_t ld0, float s0, int32_t n_split0, const float* y1, int64_t ld1,
+                                float s1, int32_t n_split1, const float* bias, float alpha, const float* gain, float eps,
+                                int32_t n, int32_t W, float* x, void* xa, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(y0 && gain && x && xa && n >= 1 && W >= 1 && ld0 >= W && (!y1 || ld1 >= W) && n_split0 >= 1 &&
+                (!y1 || n_split1 >= 1), "prl_postln_close: bad argument");
+  const int64_t st0 = (int64_t)n * ld0, st1 = (int64_t)n * ld1;
+  int th = ((W + 31) / 32) * 32;
+  const int cap = n <= 256 ? 1024 : 256;     // few rows: more threads per row; many rows: more rows per SM
+  th = th > cap ? cap : th;
+  const int keep = (size_t)W * sizeof(float) <= 40 * 1024 ? 1 : 0;
+  const size_t smem = keep ? (size_t)W * sizeof(float) : 0;
+  if (f32) PRL_CUDA(launch_pdl(postln_close_kernel<float>, dim3(n), dim3(th), smem, (cudaStream_t)st, y0, ld0, s0, n_split0, st0, y1, ld1, s1, n_split1, st1, bias, alpha, gain, eps, W, keep, x, (float*)xa));
+  else PRL_CUDA(launch_pdl(postln_close_kernel<bf16>, dim3(n), dim3(th), smem, (cudaStream_t)st, y0, ld0, s0, n_split0, st0, y1, ld1, s1, n_split1, st1, bias, alpha, gain, eps, W, keep, x, (bf16*)xa));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_attn_front(const float* P, int64_t ldp, int32_t off_q, int32_t off_k, int32_t off_v, int32_t n, int32_t H,
+                              int32_t G, int32_t dim, int32_t vdim, const float* q_bias, const float* k_bias,
+                              const float* v_bias, int32_t qk_norm, const float* q_gain, const float* k_gain,
+                              int32_t gain_period, float eps, int32_t rot, const double* freq, float mag, int32_t v_norm,
+                              int32_t v_blend, const float* v_lambda, float* v_first, const int32_t* row_pos,
+                              const int32_t* row_slot, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
+                              void* q_out, void* k_pool, void* v_pool, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(P && row_pos && row_slot && block_table && q_out && k_pool && v_pool, "prl_attn_front: NULL argument");
+  PRL_CHECK_ARG(n >= 1 && H >= 1 && G >= 1 && dim >= 1 && vdim >= 1 && page_size >= 1 && max_blocks >= 1 && rot >= 0 &&
+                rot <= dim && rot % 2 == 0 && (rot == 0 || freq) && gain_period >= 1,
+                "prl_attn_front: bad shape (H=%d G=%d dim=%d vdim=%d rot=%d)", H, G, dim, vdim, rot);
+  PRL_CHECK_ARG(v_blend >= 0 && v_blend <= 2 && (v_blend == 0 || v_first) && (v_blend != 2 || v_lambda),
+                "prl_attn_front: blending the values needs the first layer's values and the weight");
+  int warps = H + 2 * G;
+  warps = warps > 16 ? 16 : warps;
+  const size_t smem = (size_t)(rot > 0 ? rot : 1) * sizeof(float);
+  if (f32) PRL_CUDA(launch_pdl(attn_front_kernel<float>, dim3(n), dim3(32 * warps), smem, (cudaStream_t)st, P, ldp, off_q, off_k, off_v, H, G, dim, vdim, q_bias, k_bias, v_bias, qk_norm, q_gain, k_gain, gain_period, eps, rot, freq, mag, v_norm, v_blend, v_lambda, v_first, row_pos, row_slot, block_table, max_blocks, page_size, (float*)q_out, (float*)k_pool, (float*)v_pool));
+  else PRL_CUDA(launch_pdl(attn_front_kernel<bf16>, dim3(n), dim3(32 * warps), smem, (cudaStream_t)st, P, ldp, off_q, off_k, off_v, H, G, dim, vdim, q_bias, k_bias, v_bias, qk_norm, q_gain, k_gain, gain_period, eps, rot, freq, mag, v_norm, v_blend, v_lambda, v_first, row_pos, row_slot, block_table, max_blocks, page_size, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool));
+  PRL_LAUNCH_CHECK();
+  return PRL_OK;
+}
+
+extern "C" int prl_gate_heads(const void* o, int32_t o_f32, int64_t ldo, const float* g, int64_t ldg, int32_t n, int32_t H,
+                              int32_t dv, void* out, int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(o && g && out && n >= 1 && H >= 1 && dv >= 1 && ldo >= (int64_t)H * dv && ldg >= H, "prl_gate_heads: bad argument");
+  dim3 grid(n, (H * dv + 1023) / 1024);
+  cudaStream_t s = (cudaStream_t)st;
+#define PRL_GH(T, TO) PRL_CUDA(launch_pdl((gate_heads_kernel<T, TO>), grid, dim3(256), (size_t)0, s, (const TO*)o, ldo, g, ldg, H, dv, (T*)out))
+  if (f32) { if (o_f32) PRL_GH(float, float); else PRL_GH(float, bf16); }
+  else { if (o_f32) PRL_GH(bf16, float); else PRL_GH(bf16, bf16); }
+#undef PRL_GH
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

@@ -7,9 +7,10 @@
 // attention runs as one shared "key head" of size rank + rot whose value is the first `rank` channels of the same cache
 // row; the per-head value expansion W_uv,h follows on the attention output.
 //
-// Rotation ("rotate half"): channel i of the rotated part pairs with channel i + rot/2; the pair (u, v) at position p
-// becomes (u cos a - v sin a, v cos a + u sin a), a = p * freq[i], freq given in double (base^(-2i/rot)); the angle is
-// formed and its sine and cosine taken in double.
+// Rotation: channel i of the rotated part pairs with channel i + rot/2 ("rotate half"), or channel 2i with channel 2i + 1
+// (`interleaved`); the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * freq[i], freq
+// given in double (base^(-2i/rot)); the angle is formed and its sine and cosine taken in double.  A model without a
+// query latent passes q_rank = 0 and its full-size query projection to prl_latent_query directly.
 #include "prl_common.cuh"
 #include <math.h>
 
@@ -38,7 +39,8 @@ __global__ void latent_prep_kernel(const float* __restrict__ P, int64_t ldp, int
                                    int rot, const double* __restrict__ freq, const float* __restrict__ q_gain,
                                    const float* __restrict__ kv_gain, float eps, const int32_t* __restrict__ row_pos,
                                    const int32_t* __restrict__ row_slot, const int32_t* __restrict__ block_table,
-                                   int max_blocks, int page_size, T* __restrict__ cq_out, T* __restrict__ pool) {
+                                   int max_blocks, int page_size, int interleaved, T* __restrict__ cq_out,
+                                   T* __restrict__ pool) {
   pdl_wait();
   __shared__ float red[32];
   const int64_t r = blockIdx.x;
@@ -46,9 +48,11 @@ __global__ void latent_prep_kernel(const float* __restrict__ P, int64_t ldp, int
   if (slot < 0) return;
   const float* p = P + r * ldp;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) { const float v = p[off_q + c]; ss = fmaf(v, v, ss); }
-  const float inv_q = 1.f / sqrtf(block_sum(ss, red) / (float)q_rank + eps);
-  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) stf(cq_out, r * q_rank + c, p[off_q + c] * inv_q * q_gain[c]);
+  if (q_rank > 0) {
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) { const float v = p[off_q + c]; ss = fmaf(v, v, ss); }
+    const float inv_q = 1.f / sqrtf(block_sum(ss, red) / (float)q_rank + eps);
+    for (int c = threadIdx.x; c < q_rank; c += blockDim.x) stf(cq_out, r * q_rank + c, p[off_q + c] * inv_q * q_gain[c]);
+  }
   ss = 0.f;
   for (int c = threadIdx.x; c < rank; c += blockDim.x) { const float v = p[off_kv + c]; ss = fmaf(v, v, ss); }
   const float inv_c = 1.f / sqrtf(block_sum(ss, red) / (float)rank + eps);
@@ -60,9 +64,10 @@ __global__ void latent_prep_kernel(const float* __restrict__ P, int64_t ldp, int
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     double sn, cs;
     sincos((double)pos * freq[i], &sn, &cs);
-    const float u = p[off_kv + rank + i], v = p[off_kv + rank + i + half];
-    stf(dst, rank + i, u * (float)cs - v * (float)sn);
-    stf(dst, rank + i + half, v * (float)cs + u * (float)sn);
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+    const float u = p[off_kv + rank + iu], v = p[off_kv + rank + iv];
+    stf(dst, rank + iu, u * (float)cs - v * (float)sn);
+    stf(dst, rank + iv, v * (float)cs + u * (float)sn);
   }
   for (int i = 2 * half + threadIdx.x; i < rot; i += blockDim.x) stf(dst, rank + i, p[off_kv + rank + i]);   // odd size: last channel as is
 }
@@ -72,7 +77,7 @@ __global__ void latent_prep_kernel(const float* __restrict__ P, int64_t ldp, int
 // `rank` absorbed channels of the attention query [n][H][rank + rot].
 template <typename T>
 __global__ void latent_query_kernel(const float* __restrict__ Q, int64_t ldq, int H, int dim, int rot, int rank,
-                                    const double* __restrict__ freq, const int32_t* __restrict__ row_pos,
+                                    const double* __restrict__ freq, const int32_t* __restrict__ row_pos, int interleaved,
                                     T* __restrict__ q_plain, T* __restrict__ q_att) {
   pdl_wait();
   const int64_t r = blockIdx.x;
@@ -87,10 +92,11 @@ __global__ void latent_query_kernel(const float* __restrict__ Q, int64_t ldq, in
     const int h = e / half, i = e - h * half;
     double sn, cs;
     sincos((double)pos * freq[i], &sn, &cs);
-    const float u = q[h * hd + dim + i], v = q[h * hd + dim + i + half];
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : i + half;
+    const float u = q[h * hd + dim + iu], v = q[h * hd + dim + iv];
     T* dst = q_att + (r * H + h) * (rank + rot) + rank;
-    stf(dst, i, u * (float)cs - v * (float)sn);
-    stf(dst, i + half, v * (float)cs + u * (float)sn);
+    stf(dst, iu, u * (float)cs - v * (float)sn);
+    stf(dst, iv, v * (float)cs + u * (float)sn);
   }
   if (rot & 1)
     for (int h = threadIdx.x; h < H; h += blockDim.x)
@@ -121,27 +127,27 @@ typedef __nv_bfloat16 bf16;
 extern "C" int prl_latent_prep(const float* P, int64_t ldp, int32_t off_q, int32_t q_rank, int32_t off_kv, int32_t rank,
                                int32_t rot, const double* freq, const float* q_gain, const float* kv_gain, float eps,
                                const int32_t* row_pos, const int32_t* row_slot, const int32_t* block_table,
-                               int32_t max_blocks, int32_t page_size, int32_t n, void* cq_out, void* pool, int32_t f32,
-                               prl_stream_t st) {
-  PRL_CHECK_ARG(P && freq && q_gain && kv_gain && row_pos && row_slot && block_table && cq_out && pool,
+                               int32_t max_blocks, int32_t page_size, int32_t n, int32_t interleaved, void* cq_out, void* pool,
+                               int32_t f32, prl_stream_t st) {
+  PRL_CHECK_ARG(P && freq && kv_gain && row_pos && row_slot && block_table && pool && (q_rank == 0 || (q_gain && cq_out)),
                 "prl_latent_prep: NULL argument");
-  PRL_CHECK_ARG(n >= 1 && q_rank >= 1 && rank >= 1 && rot >= 0 && page_size >= 1 && max_blocks >= 1,
+  PRL_CHECK_ARG(n >= 1 && q_rank >= 0 && rank >= 1 && rot >= 0 && page_size >= 1 && max_blocks >= 1,
                 "prl_latent_prep: bad shape");
   const int th = row_threads(q_rank > rank ? q_rank : rank);
-  if (f32) PRL_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_q, q_rank, off_kv, rank, rot, freq, q_gain, kv_gain, eps, row_pos, row_slot, block_table, max_blocks, page_size, (float*)cq_out, (float*)pool));
-  else PRL_CUDA(launch_pdl(latent_prep_kernel<bf16>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_q, q_rank, off_kv, rank, rot, freq, q_gain, kv_gain, eps, row_pos, row_slot, block_table, max_blocks, page_size, (bf16*)cq_out, (bf16*)pool));
+  if (f32) PRL_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_q, q_rank, off_kv, rank, rot, freq, q_gain, kv_gain, eps, row_pos, row_slot, block_table, max_blocks, page_size, interleaved, (float*)cq_out, (float*)pool));
+  else PRL_CUDA(launch_pdl(latent_prep_kernel<bf16>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, P, ldp, off_q, q_rank, off_kv, rank, rot, freq, q_gain, kv_gain, eps, row_pos, row_slot, block_table, max_blocks, page_size, interleaved, (bf16*)cq_out, (bf16*)pool));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
 
 extern "C" int prl_latent_query(const float* Q, int64_t ldq, int32_t n, int32_t H, int32_t dim, int32_t rot, int32_t rank,
-                                const double* freq, const int32_t* row_pos, void* q_plain, void* q_att, int32_t f32,
-                                prl_stream_t st) {
+                                const double* freq, const int32_t* row_pos, int32_t interleaved, void* q_plain, void* q_att,
+                                int32_t f32, prl_stream_t st) {
   PRL_CHECK_ARG(Q && freq && row_pos && q_plain && q_att && n >= 1 && H >= 1 && dim >= 1 && rot >= 0 && rank >= 1 &&
                 ldq >= (int64_t)H * (dim + rot), "prl_latent_query: bad argument");
   const int th = row_threads(H * dim);
-  if (f32) PRL_CUDA(launch_pdl(latent_query_kernel<float>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, Q, ldq, H, dim, rot, rank, freq, row_pos, (float*)q_plain, (float*)q_att));
-  else PRL_CUDA(launch_pdl(latent_query_kernel<bf16>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, Q, ldq, H, dim, rot, rank, freq, row_pos, (bf16*)q_plain, (bf16*)q_att));
+  if (f32) PRL_CUDA(launch_pdl(latent_query_kernel<float>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, Q, ldq, H, dim, rot, rank, freq, row_pos, interleaved, (float*)q_plain, (float*)q_att));
+  else PRL_CUDA(launch_pdl(latent_query_kernel<bf16>, dim3(n), dim3(th), (size_t)0, (cudaStream_t)st, Q, ldq, H, dim, rot, rank, freq, row_pos, interleaved, (bf16*)q_plain, (bf16*)q_att));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }

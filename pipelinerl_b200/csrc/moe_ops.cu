@@ -2,7 +2,8 @@
 // of rows each expert gets stays on the device, so the whole layer can sit in a CUDA graph.
 //
 //   1. route:  per row, the `top` experts with the largest router logits (ties: the lower index), each with the weight
-//              sigmoid(logit) or softmax over the chosen; choice c of row t is the PAIR c * n + t.
+//              sigmoid(logit) or softmax over the chosen; an optional bias per expert joins the logits first; choice c
+//              of row t is the PAIR c * n + t.
 //   2. group:  a stable counting sort of the pairs by expert (one CTA): perm[s] = pair at sorted place s, and a table
 //              of row tiles (expert, first sorted place, rows <= 64) that the GEMMs walk; its length stays on the device.
 //   3. grouped GEMM (twice):  C[row] = A[row'] * W_e^T for every tile, W_e = W + e * expert_stride.  The first product
@@ -32,8 +33,8 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 
 // one warp per row; E up to 32 * kMaxPerLane
 constexpr int kMaxPerLane = 32;
-__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, int n, int E, int top, int softmax_weights,
-                                 int32_t* __restrict__ sel, float* __restrict__ wsel) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ bias, int n, int E,
+                                 int top, int softmax_weights, int32_t* __restrict__ sel, float* __restrict__ wsel) {
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -48,7 +49,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
       const int e = lane + 32 * j;
       if (e >= E) break;
       if (taken >> j & 1u) continue;
-      const float v = z[e];
+      const float v = z[e] + (bias ? bias[e] : 0.f);
       if (v > best) { best = v; arg = e; }        // ascending e: the lower index wins a tie inside a lane
     }
 #pragma unroll
@@ -70,7 +71,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
     for (int j = 0; j < kMaxPerLane; ++j) {
       const int e = lane + 32 * j;
       if (e >= E) break;
-      all += expf(z[e] - zsel_max);
+      all += expf(z[e] + (bias ? bias[e] : 0.f) - zsel_max);
     }
     denom = warp_sum(all);
   }
@@ -82,8 +83,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int64_t ld, i
 // take experts in turn, a lane sums every 32nd channel, then the warp's shuffle tree: a fixed order), then the top-k
 // pass of moe_route_kernel over the logits in shared memory.
 template <typename TX, typename TW>
-__global__ void __launch_bounds__(256) moe_router_kernel(const TX* __restrict__ x, const TW* __restrict__ Wr, int n, int W, int E,
-                                                         int top, int softmax_weights, int32_t* __restrict__ sel,
+__global__ void __launch_bounds__(256) moe_router_kernel(const TX* __restrict__ x, const TW* __restrict__ Wr,
+                                                         const float* __restrict__ bias, int n, int W, int E, int top,
+                                                         int softmax_weights, int32_t* __restrict__ sel,
                                                          float* __restrict__ wsel) {
   pdl_wait();
   extern __shared__ float rsm[];       // [W] the row | [E] logits
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const TX* __restrict__ 
     for (int c = lane; c < W; c += 32) a = fmaf(xs[c], to_f32(w[c]), a);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-    if (lane == 0) z[e] = a;
+    if (lane == 0) z[e] = a + (bias ? bias[e] : 0.f);
   }
   __syncthreads();
   if (warp != 0) return;
@@ -392,14 +394,14 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int64_t prl_moe_max_tiles(int64_t pairs, int32_t experts) { return (pairs + kTile - 1) / kTile + experts; }
 
-extern "C" int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t experts, int32_t top,
+extern "C" int prl_moe_route(const float* logits, int64_t ld, const float* bias, int32_t n, int32_t experts, int32_t top,
                              int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm, int32_t* meta,
                              int32_t* tiles, prl_stream_t st) {
   PRL_CHECK_ARG(logits && sel && wsel && perm && meta && tiles, "prl_moe_route: NULL argument");
   PRL_CHECK_ARG(n >= 1 && experts >= 1 && experts <= 32 * kMaxPerLane && top >= 1 && top <= experts && ld >= experts,
                 "prl_moe_route: bad shape (experts=%d top=%d; at most %d experts)", experts, top, 32 * kMaxPerLane);
   cudaStream_t s = (cudaStream_t)st;
-  PRL_CUDA(launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), (size_t)0, s, logits, ld, n, experts, top, softmax_weights, sel, wsel));
+  PRL_CUDA(launch_pdl(moe_route_kernel, dim3((n + 7) / 8), dim3(256), (size_t)0, s, logits, ld, bias, n, experts, top, softmax_weights, sel, wsel));
   PRL_LAUNCH_CHECK();
   PRL_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), (size_t)(2 * experts * sizeof(int32_t)), s, (const int32_t*)sel, n * top, experts, perm, meta, tiles));
   PRL_LAUNCH_CHECK();
@@ -408,7 +410,7 @@ extern "C" int prl_moe_route(const float* logits, int64_t ld, int32_t n, int32_t
 
 // Router product, choice and grouping in two launches: x [n, W] and the router matrix [experts, W] in fp32 or bf16.
 // Needs (W + experts) * 4 bytes of shared memory; returns PRL_ERR_INVALID beyond 160 KB (use prl_gemm_any + prl_moe_route).
-extern "C" int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, int32_t n, int32_t W,
+extern "C" int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, int32_t w_is_f32, const float* bias, int32_t n, int32_t W,
                               int32_t experts, int32_t top, int32_t softmax_weights, int32_t* sel, float* wsel, int32_t* perm,
                               int32_t* meta, int32_t* tiles, prl_stream_t st) {
   PRL_CHECK_ARG(x && Wr && sel && wsel && perm && meta && tiles, "prl_moe_router: NULL argument");
@@ -421,7 +423,7 @@ extern "C" int prl_moe_router(const void* x, int32_t x_is_f32, const void* Wr, i
 #define PRL_RT(TX, TW, I)                                                                                              \
   do {                                                                                                                 \
     if (smem > 48 * 1024) PRL_CUDA(ensure_smem(moe_router_kernel<TX, TW>, (int)smem, attr[I]));                        \
-    PRL_CUDA(launch_pdl((moe_router_kernel<TX, TW>), dim3(n), dim3(256), smem, s, (const TX*)x, (const TW*)Wr, n, W, experts, top, \
+    PRL_CUDA(launch_pdl((moe_router_kernel<TX, TW>), dim3(n), dim3(256), smem, s, (const TX*)x, (const TW*)Wr, bias, n, W, experts, top, \
                         softmax_weights, sel, wsel));                                                                  \
   } while (0)
   if (x_is_f32 && w_is_f32) PRL_RT(float, float, 0);

@@ -52,6 +52,19 @@ class AttnSpec:
     bias: bool = False          # q and k projections have biases
     value_is_key: bool = False  # no value projection: the value is the key as projected (before its norm)
     gate: bool = True           # sigmoid output gate from its own projection
+    # what follows belongs to the layers normed after the sum (HybridConfig.block == "post_ln")
+    gate_per_head: bool = False  # the gate projection has one row per head instead of one per output channel
+    head_gain: bool = False     # the per-head norms of q and k have a gain of head size shared by all heads (q.norm, k.norm)
+    v_bias: bool = False        # the value projection has a bias
+    o_bias: bool = False        # the output projection has a bias
+    rot_half: bool = False      # rotated pairs are (i, i + rot_dims / 2) instead of (2i, 2i + 1)
+    rot_scaling: tuple | None = None   # YaRN: (factor, original length, fast turns, slow turns)
+    v_norm: bool = False        # every value head divided by its root mean square (no gain) before it is cached
+    v_mix: int = 0              # 1: this layer's values are kept for later layers; 2: v <- (1 - l) v + l v_first, l = `vmix`
+    sink: bool = False          # a learned logit per head in the softmax denominator (no key, no value)
+    weights: str = "softmax"    # "sigmoid": weight = sigmoid(score + pb[h]) for every visible key, not normalised
+    q_temp: tuple = (0.0, 1.0)  # (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1)
+    talking: bool = False       # the heads' weights are mixed by the matrix `talk` [heads, heads] before they meet the values
 
 
 @dataclass(frozen=True)
@@ -86,6 +99,31 @@ class LatentAttnSpec:
     rot_base: float
     scale: float
     sink: bool = True   # a learned logit per head in the softmax denominator (no key, no value)
+    window: int = 0     # > 0: a query sees only the last `window` positions (itself included)
+    interleaved: bool = False   # rotated pairs are (2i, 2i + 1) instead of (i, i + rot_dim / 2)
+    gate: bool = False  # element-wise sigmoid gate on the concatenated heads, from its own projection `g`
+    # q_rank == 0: the query comes straight from the layer's input (tensor `q`), without a latent
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule S <- g S; d = beta (v - S^T k); S <- S + k d^T; o = S^T q: short causal convolutions + SiLU on
+    q, k, v, unit q (times dim^-1/2) and k, beta = sigmoid(.), one decay g = exp(-exp(A_log) softplus(. + dt_bias)) per
+    head, per-head RMS norm with a gain of size vdim times a SiLU gate.  `kv_heads` q / k heads serve `heads` value heads."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    unit_eps: float = 1e-6
+
+    @property
+    def conv_channels(self) -> int:
+        return 2 * self.kv_heads * self.dim + self.heads * self.vdim
+
+    @property
+    def in_rows(self) -> int:   # [q | k | v | b | a | g]
+        return self.conv_channels + 2 * self.heads + self.heads * self.vdim
 
 
 @dataclass(frozen=True)
@@ -108,6 +146,8 @@ class MoeSpec:
     shared_ff: int = 0          # 0: no shared expert
     shared_limit: float = 0.0
     score: str = "sigmoid"      # "sigmoid" of the chosen logit | "softmax_all": softmax over ALL experts, not renormalised
+                                # | "softmax_top": softmax over the chosen logits only
+    router_bias: bool = False   # the router logits get a bias per expert (`router.b`) before the choice
     weight_on: str = "input"    # the score scales the expert's "input" (clamped unit) or its "output" (plain SiLU unit)
     weight_scale: float = 1.0   # constant factor on the scores
 
@@ -156,6 +196,8 @@ class MlpSpec:
 class LayerSpec:
     kind: str                       # "gla" | "parallel" (attention || state space) | "parallel_lin" (attention || lightning) | "mlstm"
                                     # | "latent" (latent attention) | "delta" (delta-rule memory): the multi-stream program
+                                    # | "attention" | "latent_attention" | "sigmoid_delta" (attention without a softmax ||
+                                    #   gated delta rule): the layers normed after the sum
     weights_of: int                 # index of the layer whose tensors this layer uses (its own index if it has its own)
     gla: GlaSpec | None = None
     attn: AttnSpec | None = None
@@ -172,6 +214,7 @@ class LayerSpec:
     layer_scale: bool = False       # sublayer results times a per-channel vector (ls1 / ls2)
     gated: bool = False             # sublayer results times sigmoid(W_rg h + b) of the sublayer's own input
     hyper: bool = False             # learned read / write / mixing weights over the residual streams (hc1.* / hc2.*)
+    gdelta: GatedDeltaSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -188,6 +231,9 @@ class HybridConfig:
     norm_kind: str = "rms"          # "tanh": tanh(alpha x) * gain + shift, no statistics (tensors <name>, .b, .alpha)
     streams: int = 1                # parallel copies of the residual ("tanh" program only)
     pair_embed: tuple | None = None  # (buckets, mul_prev, mul_cur): hashed (previous, current) token table `bigram`
+    block: str = "out_norm"         # "post_ln": x <- norm(skip_scale * x + f(x)) for every sublayer, f reads x itself
+    skip_scale: float = 1.0
+    tied_head: bool = False         # logits = embed . x: no separate `head` tensor
 
     @property
     def head_rows(self) -> int:
@@ -359,6 +405,66 @@ class HybridConfig:
         cfg.validate()
         return cfg
 
+    # ---- the "Kolotar" reading of config.json ---------------------------------------------------------------------
+    @staticmethod
+    def from_kolotar(d: dict, tensor_shapes: dict | None = None) -> "HybridConfig":
+        """config.json of a Kolotar checkpoint: every sublayer normed after the sum with a weighted skip
+        (`postln_alpha`), layers of three kinds in any order, routed experts everywhere, logits from the embedding
+        table.  Which optional tensors a layer has (biases, sink, gate, router bias) is read off the tensor names when
+        a file is at hand."""
+        shapes = tensor_shapes or {}
+        layers, first_vmix = [], None
+        for i, L in enumerate(d["layers"]):
+            m, f, mlp = L["mixer"], L.get("mlp"), None
+            has = (lambda name: f"l{i}.{name}" in shapes) if shapes else (lambda name: True)
+            if f is not None:
+                if f.get("kind", "moe") != "moe":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f.get('kind')!r}")
+                r = f["router"]
+                moe = MoeSpec(int(r["experts"]), int(r["top"]), int(f["expert"]["ff"]), 0.0, score="softmax_top",
+                              weight_on="output", router_bias=has("mlp.router.b"))
+                mlp = MlpSpec(ff=0, limit=0.0, kind="moe", moe=moe)
+            if L["type"] == "attention":
+                rot = m.get("rot") or {}
+                sc = rot.get("scaling")
+                mix = 0
+                if m.get("v_mix"):
+                    mix = 2 if first_vmix is not None else 1
+                    first_vmix = i if first_vmix is None else first_vmix
+                attn = AttnSpec(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m.get("vdim", m["dim"])),
+                                int(rot.get("dims", 0)), float(rot.get("base", 10000.0)), float(m["scale"]),
+                                window=int((m.get("mask") or {}).get("size", 0)), head_norm=True, head_gain=True,
+                                bias=has("mix.q.b"), v_bias=has("mix.v.b"), o_bias=has("mix.o.b"), gate=has("mix.g"),
+                                gate_per_head=True, rot_half=True,
+                                rot_scaling=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None,
+                                v_norm=True, v_mix=mix, sink=has("mix.sink"))
+                layers.append(LayerSpec("attention", i, attn=attn, mlp=mlp))
+            elif L["type"] == "latent_attention":
+                rot = m.get("rot") or {}
+                if int(rot.get("dims", m["rot_dim"])) != int(m["rot_dim"]):
+                    raise ValueError(f"layer {i}: the rotated part has {m['rot_dim']} channels but rot.dims = {rot.get('dims')}")
+                lat = LatentAttnSpec(int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"]), 0,
+                                     float(rot.get("base", 10000.0)), float(m["scale"]), sink=False,
+                                     window=int((m.get("mask") or {}).get("size", 0)), interleaved=True, gate=has("mix.g"))
+                layers.append(LayerSpec("latent_attention", i, latent=lat, mlp=mlp))
+            elif L["type"] == "parallel":
+                a, r = m["left"], m["right"]
+                qt = a.get("q_temp") or {}
+                attn = AttnSpec(int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a.get("vdim", a["dim"])),
+                                0, 10000.0, float(a["scale"]), softcap=float(a.get("softcap", 0.0)), gate=False,
+                                weights="sigmoid", q_temp=(float(qt.get("coef", 0.0)), float(qt.get("every", 1.0))),
+                                talking=has("mix.left.talk"))
+                gd = GatedDeltaSpec(int(r["heads"]), int(r.get("kv_heads", r["heads"])), int(r["dim"]), int(r["vdim"]),
+                                    int(r["conv"]))
+                layers.append(LayerSpec("sigmoid_delta", i, attn=attn, gdelta=gd, left_scale=float(m["left_scale"]),
+                                        right_scale=float(m["right_scale"]), mlp=mlp))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {L['type']!r}")
+        cfg = HybridConfig(int(d["vocab"]), int(d["width"]), float(d["norm"]["eps"]), 1.0, tuple(layers), block="post_ln",
+                           skip_scale=float(d["postln_alpha"]), tied_head=True)
+        cfg.validate()
+        return cfg
+
     def validate(self) -> None:
         if self.norm_kind == "tanh":
             if not 1 <= self.streams <= 8 or any(L.kind not in ("latent", "delta") for L in self.layers):
@@ -367,7 +473,31 @@ class HybridConfig:
                 raise ValueError(f"bad token-pair table {self.pair_embed}")
         elif any(L.kind in ("latent", "delta") for L in self.layers):
             raise ValueError("latent-attention and delta-rule layers belong to the multi-stream program (norm_kind 'tanh')")
+        post = ("attention", "latent_attention", "sigmoid_delta")
+        if any((L.kind in post) != (self.block == "post_ln") for L in self.layers):
+            raise ValueError(f"layers of the kinds {post} and no others run in the 'post_ln' block")
+        mixing = [L.attn for L in self.layers if L.kind == "attention" and L.attn.v_mix]
+        if mixing and (len({a.kv_heads * a.vdim for a in mixing}) != 1 or [a.v_mix for a in mixing] != [1] + [2] * (len(mixing) - 1)):
+            raise ValueError("layers that blend their values have one value size; the first keeps its values, the others blend")
         for i, L in enumerate(self.layers):
+            if L.kind in post:
+                if L.mlp is not None and L.mlp.kind != "moe":
+                    raise ValueError(f"layer run {i}: the 'post_ln' block has routed feed-forwards")
+                if L.mlp is not None and not 1 <= L.mlp.moe.top <= L.mlp.moe.experts <= 1024:
+                    raise ValueError(f"layer run {i}: bad router {L.mlp.moe}")
+                if L.kind == "latent_attention":
+                    a = L.latent
+                    if a.rot_dim % 2 or a.kv_rank + a.rot_dim > 1024 or min(a.heads, a.dim, a.vdim, a.kv_rank) < 1 or a.q_rank or a.window < 0:
+                        raise ValueError(f"layer run {i}: bad latent-attention geometry {a}")
+                    continue
+                a = L.attn
+                if a.heads % a.kv_heads or a.rot_dims % 2 or a.rot_dims > a.dim or a.dim > 1024 or a.vdim > 512 or a.window < 0:
+                    raise ValueError(f"layer run {i}: bad attention geometry {a}")
+                if L.kind == "sigmoid_delta":
+                    g = L.gdelta
+                    if g.heads % g.kv_heads or not 1 <= g.conv <= 16 or g.dim > 256 or min(g.dim, g.vdim) < 1:
+                        raise ValueError(f"layer run {i}: bad gated-delta geometry {g}")
+                continue
             if L.kind == "latent":
                 a = L.latent
                 if a.rot_dim % 2 or a.kv_rank > 512 or a.kv_rank + a.rot_dim > 1024 or min(a.heads, a.dim, a.vdim, a.q_rank) < 1:
@@ -419,6 +549,9 @@ class HybridConfig:
             if L.kind in ("latent", "delta"):
                 out += [(name, shape) for name, shape, _ in self._stream_layer_tensors(i, L)]
                 continue
+            if self.block == "post_ln":
+                out += [(name, shape) for name, shape, _ in self._postln_layer_tensors(i, L)]
+                continue
             if L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
@@ -465,7 +598,9 @@ class HybridConfig:
                     out.append((p + "norm2b", (W,)))
         if self.loop_times:
             out += [("loop.in", (W, 2 * W)), ("loop.step", (self.loop_times, W))]
-        out += [("embed", (self.vocab_size, W)), ("final.norm", (W,)), ("head", (self.vocab_size, W))]
+        out += [("embed", (self.vocab_size, W)), ("final.norm", (W,))]
+        if not self.tied_head:
+            out.append(("head", (self.vocab_size, W)))
         if self.norm_kind == "tanh":
             out += [("final.norm.b", (W,)), ("final.norm.alpha", (1,))]
         if self.pair_embed is not None:
@@ -514,6 +649,65 @@ class HybridConfig:
                 one("rg2", (W, W))
         return out
 
+    def _postln_layer_tensors(self, i: int, L: LayerSpec) -> list:
+        """(fused tensor, shape, [(checkpoint tensor, rows)] in row order) of a layer of the 'post_ln' block.  All
+        projections that read the layer's input are ONE fused tensor `mix.in` (both mixers of a parallel layer, gates
+        included), the biases of its rows one vector."""
+        W, p, out = self.width, f"l{i}.", []
+        one = lambda name, shape: out.append((p + name, shape, [(p + name, shape[0])]))
+        if L.kind == "attention":
+            a = L.attn
+            nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+            parts = [(p + "mix.q", nq), (p + "mix.k", nk), (p + "mix.v", nv)] + ([(p + "mix.g", a.heads)] if a.gate else [])
+            out.append((p + "mix.in", (sum(n for _, n in parts), W), parts))
+            if a.bias:
+                out.append((p + "mix.qk.b", (nq + nk,), [(p + "mix.q.b", nq), (p + "mix.k.b", nk)]))
+            if a.v_bias:
+                one("mix.v.b", (nv,))
+            if a.head_gain:
+                one("mix.q.norm", (a.dim,)); one("mix.k.norm", (a.dim,))
+            if a.v_mix:
+                one("mix.vmix", (1,))
+            if a.sink:
+                one("mix.sink", (a.heads,))
+            one("mix.o", (W, a.heads * a.vdim))
+            if a.o_bias:
+                one("mix.o.b", (W,))
+        elif L.kind == "latent_attention":
+            a = L.latent
+            parts = [(p + "mix.q", a.heads * (a.dim + a.rot_dim)), (p + "mix.dkv", a.kv_rank + a.rot_dim)]
+            parts += [(p + "mix.g", a.heads * a.vdim)] if a.gate else []
+            out.append((p + "mix.in", (sum(n for _, n in parts), W), parts))
+            one("mix.dkv.norm", (a.kv_rank,)); one("mix.uk", (a.heads * a.dim, a.kv_rank))
+            one("mix.uv", (a.heads * a.vdim, a.kv_rank)); one("mix.o", (W, a.heads * a.vdim))
+        else:
+            a, g = L.attn, L.gdelta
+            nq, nk, nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+            gq, gv = g.kv_heads * g.dim, g.heads * g.vdim
+            parts = [(p + "mix.left.q", nq), (p + "mix.left.k", nk), (p + "mix.left.v", nv), (p + "mix.right.q", gq),
+                     (p + "mix.right.k", gq), (p + "mix.right.v", gv), (p + "mix.right.b", g.heads), (p + "mix.right.a", g.heads),
+                     (p + "mix.right.g", gv)]
+            out.append((p + "mix.in", (sum(n for _, n in parts), W), parts))
+            one("mix.left.q.norm", (nq,)); one("mix.left.k.norm", (nk,)); one("mix.left.pb", (a.heads,))
+            if a.talking:
+                one("mix.left.talk", (a.heads, a.heads))
+            one("mix.left.o", (W, a.heads * a.vdim))
+            out.append((p + "mix.right.conv", (g.conv_channels, g.conv),
+                        [(p + "mix.right.q.conv", gq), (p + "mix.right.k.conv", gq), (p + "mix.right.v.conv", gv)]))
+            one("mix.right.A_log", (g.heads,)); one("mix.right.dt_bias", (g.heads,)); one("mix.right.norm", (g.vdim,))
+            one("mix.right.o", (W, gv))
+        one("norm1", (W,))
+        if L.mlp is not None:
+            e = L.mlp.moe
+            one("mlp.router", (e.experts, W))
+            if e.router_bias:
+                one("mlp.router.b", (e.experts,))
+            out.append((p + "mlp.experts.gate_up", (e.experts * 2 * e.ff, W),
+                        [(f"{p}mlp.e{k}.{part}", e.ff) for k in range(e.experts) for part in ("gate", "up")]))
+            out.append((p + "mlp.experts.down", (e.experts * W, e.ff), [(f"{p}mlp.e{k}.down", W) for k in range(e.experts)]))
+            one("norm2", (W,))
+        return out
+
     def checkpoint_slices(self) -> dict[str, tuple[str, int, int]]:
         """checkpoint tensor name -> (fused tensor, first row, rows)."""
         m: dict[str, tuple[str, int, int]] = {}
@@ -527,6 +721,10 @@ class HybridConfig:
             p = f"l{i}."
             if L.kind in ("latent", "delta"):
                 for fused, _, parts in self._stream_layer_tensors(i, L):
+                    rows(fused, parts)
+                continue
+            if self.block == "post_ln":
+                for fused, _, parts in self._postln_layer_tensors(i, L):
                     rows(fused, parts)
                 continue
             if L.kind == "gla":
@@ -593,7 +791,8 @@ class HybridConfig:
             m["loop.step"] = ("loop.step", 0, self.loop_times)
         m["embed"] = ("embed", 0, self.vocab_size)
         m["final.norm"] = ("final.norm", 0, self.width)
-        m["head"] = ("head", 0, self.vocab_size)
+        if not self.tied_head:
+            m["head"] = ("head", 0, self.vocab_size)
         if self.norm_kind == "tanh":
             m["final.norm.b"] = ("final.norm.b", 0, self.width)
             m["final.norm.alpha"] = ("final.norm.alpha", 0, 1)
@@ -609,6 +808,11 @@ class HybridConfig:
                        torch.full(view.shape, 1.0 / self.streams if leaf == "in" else 1.0))
         elif leaf == "alpha":
             view.fill_(0.5)
+        elif leaf == "vmix":
+            view.fill_(0.5)
+        elif leaf == "talk":
+            view.copy_((torch.eye(view.shape[0], device=view.device)
+                        + 0.1 * torch.randn(view.shape, generator=gen, device=view.device)).to(view.dtype))
         elif leaf in ("ls1", "ls2"):
             view.fill_(1.0)
         elif leaf in ("norm1", "norm2", "norm1b", "norm2b") or name == "final.norm":
@@ -642,6 +846,25 @@ class HybridConfig:
         return n
 
 
+def rotary_table(dims: int, base: float, scaling: tuple | None = None):
+    """(frequencies of the dims / 2 rotated pairs, factor on cos and sin).  Plain: base^(-2i/dims), factor 1.  With YaRN
+    scaling (factor, original length, fast turns, slow turns): pairs that complete more than `fast` turns over the
+    original length keep their frequency, those below `slow` turns are divided by `factor`, a linear ramp over the pair
+    index in between; cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    half = dims // 2
+    f = [base ** (-2.0 * i / dims) for i in range(half)]
+    if not scaling or not half:
+        return f, 1.0
+    factor, orig, fast, slow = scaling
+    at = lambda turns: dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo, hi = max(math.floor(at(fast)), 0), min(math.ceil(at(slow)), dims - 1)
+    out = []
+    for i in range(half):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f[i] / factor * ramp + f[i] * (1.0 - ramp))
+    return out, 0.1 * math.log(factor) + 1.0
+
+
 class _Rows:
     """Activation buffers and ragged-row metadata for up to `n` rows."""
 
@@ -650,8 +873,30 @@ class _Rows:
         W = cfg.width
         wide_p, wide_aux, wide_o, wide_o2, wide_q, wide_f = W, 1, 1, 1, 1, 1
         wide_gate, moe_pairs, moe_ff, moe_experts = 0, 0, 1, 1     # mLSTM gate heads; routed pairs per row, expert width
+        wide_vfirst, wide_prep = 0, 0                               # values kept for later layers; gated-delta vectors
         for L in cfg.layers:
-            if L.kind == "gla":
+            if L.kind == "attention":
+                a = L.attn
+                nq = a.heads * a.dim
+                wide_p = max(wide_p, nq + a.kv_heads * (a.dim + a.vdim) + a.heads)
+                wide_q, wide_o = max(wide_q, nq), max(wide_o, a.heads * a.vdim)
+                if a.v_mix:
+                    wide_vfirst = max(wide_vfirst, a.kv_heads * a.vdim)
+            elif L.kind == "latent_attention":
+                a = L.latent               # buffer roles: see HybridEngine._latent_direct_mixer
+                wide_p = max(wide_p, a.heads * (a.dim + a.rot_dim) + a.kv_rank + a.rot_dim + a.heads * a.vdim)
+                wide_o = max(wide_o, a.heads * a.kv_rank, a.heads * a.vdim)
+                wide_o2 = max(wide_o2, a.heads * a.dim, a.heads * a.vdim)
+                wide_q = max(wide_q, a.heads * (a.kv_rank + a.rot_dim))
+            elif L.kind == "sigmoid_delta":
+                a, g = L.attn, L.gdelta
+                nq = a.heads * a.dim
+                wide_p = max(wide_p, nq + a.kv_heads * (a.dim + a.vdim) + g.in_rows)
+                wide_q, wide_aux = max(wide_q, nq), max(wide_aux, g.conv_channels)
+                wide_o = max(wide_o, a.heads * a.vdim, g.heads * g.vdim)
+                wide_o2 = max(wide_o2, g.heads * g.vdim)
+                wide_prep = max(wide_prep, 5 * g.heads * g.dim)
+            elif L.kind == "gla":
                 g = L.gla
                 nq, nv = g.heads * g.dim, g.heads * g.vdim
                 wide_p = max(wide_p, 2 * nq + 2 * nv + g.rank)
@@ -688,7 +933,7 @@ class _Rows:
                 wide_aux, wide_o = max(wide_aux, s.conv_channels), max(wide_o, a.heads * a.vdim)
                 wide_o2, wide_q = max(wide_o2, s.inner), max(wide_q, nq)
             if L.mlp is not None:
-                wide_p, wide_f = max(wide_p, 2 * L.mlp.ff), max(wide_f, L.mlp.ff)
+                wide_p, wide_f = max(wide_p, 2 * L.mlp.ff), max(wide_f, max(L.mlp.ff, 1))
                 if L.mlp.kind == "moe":
                     e = L.mlp.moe
                     wide_p = max(wide_p, e.top * 2 * e.ff)
@@ -712,6 +957,10 @@ class _Rows:
         self.y1 = torch.zeros(ny, **f32)
         self.q = torch.zeros(n * wide_q, dtype=T, device=d)
         self.act = torch.zeros(n * wide_f, dtype=T, device=d)
+        if wide_vfirst:                                         # the first value-blending layer's values of the batch's rows
+            self.vfirst = torch.zeros(n * wide_vfirst, **f32)
+        if wide_prep:                                           # u | a u | w | k | r of the gated delta rule
+            self.dprep = torch.zeros(n * wide_prep, **f32)
         if cfg.loop_times:                                      # the embedding output and [x | x0], operand type
             self.x0a = torch.zeros(n * W, dtype=T, device=d)
             self.xcat = torch.zeros(n * 2 * W, dtype=T, device=d)
@@ -781,8 +1030,21 @@ class HybridEngine(EngineCore):
         self._head_tables: dict = {}
         if cfg.pair_embed is not None:                   # the last token of the sequence's previous portion
             self.prev_token = self.states.add("prev_token", (1,), dtype=torch.int32)
+        self.rot_mag: dict[int, float] = {}
         for i, L in enumerate(cfg.layers):               # one cache / state per layer RUN, also where weights are shared
-            if L.kind == "latent":
+            if L.kind in ("attention", "sigmoid_delta"):
+                a = L.attn
+                self.k_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.dim, dtype=self.op_dtype, device=d)
+                self.v_pool[i] = torch.zeros(self.n_pages, a.kv_heads, PAGE_SIZE, a.vdim, dtype=self.op_dtype, device=d)
+                self.tc_attn[i] = False
+                f, self.rot_mag[i] = rotary_table(a.rot_dims, a.rot_base, a.rot_scaling)
+                self.rot_freq[i] = torch.tensor(f or [0.0], dtype=torch.float64, device=d)
+                if L.kind == "sigmoid_delta":
+                    g = L.gdelta
+                    self.conv_state[i] = self.states.add(f"l{i}.conv", (g.conv_channels, max(g.conv - 1, 1)))
+                    n = int(lib.prl_delta_state_floats(g.heads, g.dim, g.vdim))
+                    self.delta_state[i] = self.states.add(f"l{i}.delta", (n,))
+            elif L.kind in ("latent", "latent_attention"):
                 a = L.latent                             # one row per token: [latent | rotated shared key part]
                 self.lat_pool[i] = torch.zeros(self.n_pages, PAGE_SIZE, a.kv_rank + a.rot_dim, dtype=self.op_dtype, device=d)
                 f = [a.rot_base ** (-2.0 * k / a.rot_dim) for k in range(a.rot_dim // 2)] or [0.0]
@@ -833,16 +1095,20 @@ class HybridEngine(EngineCore):
         # fp32 copies of the small parameter vectors (gains, biases, taps, per-head constants): exact for bf16 weights
         self.vec: dict[str, torch.Tensor] = {}
         for name, shape in cfg.fused_shapes():
-            if len(shape) == 1 or name.endswith("mix.right.conv") or name == "loop.step" or name.endswith(".mix") and ".hc" in name:
+            if (len(shape) == 1 or name.endswith("mix.right.conv") or name.endswith("mix.left.talk") or name == "loop.step"
+                    or name.endswith(".mix") and ".hc" in name):
                 self.vec[name] = torch.zeros(shape, dtype=torch.float32, device=d)
         # per-head transposes W_uk,h^T [kv_rank, dim] of the latent layers' key expansion (operand type): the B operand
         # of the product that absorbs the expansion into the query.  Refreshed with the small vectors on a weight flip.
         self.uk_t = {L.weights_of: torch.zeros(L.latent.heads, L.latent.kv_rank, L.latent.dim, dtype=self.op_dtype, device=d)
-                     for L in cfg.layers if L.kind == "latent"}
+                     for L in cfg.layers if L.latent is not None}
         if cfg.norm_kind == "tanh":                      # stream weights of layers without their own: the plain residual sum
             S = cfg.streams
             self.stream_ones = torch.ones(S, dtype=torch.float32, device=d)
             self.stream_eye = torch.eye(S, dtype=torch.float32, device=d)
+        conv_ch = max([L.gdelta.conv_channels for L in cfg.layers if L.gdelta is not None], default=0)
+        if conv_ch:                                      # the short convolutions of the gated delta rule have no bias
+            self.zero_bias = torch.zeros(conv_ch, dtype=torch.float32, device=d)
         if cfg.positions == "sinusoid":
             W = cfg.width
             self.pos_freq = torch.tensor([10000.0 ** (-2.0 * k / W) for k in range((W + 1) // 2)], dtype=torch.float64, device=d)
@@ -855,7 +1121,7 @@ class HybridEngine(EngineCore):
                 self.attn_splits[i] = int(lib.prl_paged_attn_splits(B, a.kv_heads, self.max_seq_len))
                 ws = max(ws, int(lib.prl_paged_attn_workspace_bytes(B, a.heads, self.attn_splits[i])))
         for L in cfg.layers:                              # latent attention: the key splits' shares of a batch of single tokens
-            if L.kind == "latent":
+            if L.latent is not None:
                 for n_seg in range(1, max(B, 4) + 1):     # the split count falls as the batch grows; the product need not
                     ws = max(ws, int(lib.prl_attn_latent_workspace_bytes(n_seg, L.latent.heads, L.latent.kv_rank)))
         self.attn_ws = torch.zeros(max(ws, 16), dtype=torch.uint8, device=d)
@@ -877,6 +1143,10 @@ class HybridEngine(EngineCore):
             H, r, dm = t.shape
             t.copy_(self.arena.view(f"l{j}.mix.uk").view(H, dm, r).transpose(1, 2))
 
+    @property
+    def head_name(self) -> str:
+        return "embed" if self.cfg.tied_head else "head"
+
     @staticmethod
     def scan_geometry(L) -> list:
         """(heads, key size, value columns) of every matrix-state recurrence of a layer."""
@@ -886,8 +1156,8 @@ class HybridEngine(EngineCore):
             return [(L.mlstm.heads, L.mlstm.dim, L.mlstm.vdim + 1)]
         if L.kind == "parallel_lin":
             return [(L.lin.heads, L.lin.dim, L.lin.vdim)]
-        if L.kind in ("latent", "delta"):
-            return []                      # the delta rule has a scan of its own (prl_delta_scan), walked token by token
+        if L.kind in ("latent", "delta", "attention", "latent_attention", "sigmoid_delta"):
+            return []                      # the delta rules have a scan of their own (delta_scan.cu), walked token by token
         return [(L.ssd.heads, L.ssd.state, L.ssd.vdim)]
 
     def kv_bytes_per_token(self) -> int:
@@ -919,6 +1189,8 @@ class HybridEngine(EngineCore):
         cfg, lib, st, f32 = self.cfg, self.lib, self._st, int(self.f32)
         if cfg.norm_kind == "tanh":
             return self._stream_layers(R, n, ns, max_q, row_pos, seg_pos0, trace)
+        if cfg.block == "post_ln":
+            return self._postln_layers(R, n, ns, max_q, row_pos, seg_pos0, trace)
         W, eps, vec = cfg.width, cfg.eps, self.vec
         seg_start, seg_len, seg_slot = R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr()
         P, x, xa = R.P.data_ptr(), R.x.data_ptr(), R.xa.data_ptr()
@@ -1088,14 +1360,16 @@ class HybridEngine(EngineCore):
         lib, st, W, f32 = self.lib, self._st, self.cfg.width, int(self.f32)
         pairs = n * e.top
         route = (R.sel.data_ptr(), R.wsel.data_ptr(), R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), st)
-        mode = 2 if e.score == "softmax_all" else 0     # weights: sigmoid of the chosen logit | softmax over all experts
+        # weights: sigmoid of the chosen logit | softmax over the chosen | softmax over all experts
+        mode = {"sigmoid": 0, "softmax_top": 1, "softmax_all": 2}[e.score]
+        bias = self.vec[w + "mlp.router.b"].data_ptr() if e.router_bias else None
         if (W + e.experts) * 4 <= 160 * 1024 and not self.unfused_router:
-            _lib.check(lib.prl_moe_router(R.xa.data_ptr(), f32, self.arena.ptr(w + "mlp.router"), f32, n, W, e.experts, e.top, mode,
-                                          *route))
+            _lib.check(lib.prl_moe_router(R.xa.data_ptr(), f32, self.arena.ptr(w + "mlp.router"), f32, bias, n, W, e.experts, e.top,
+                                          mode, *route))
         else:
             _lib.check(lib.prl_gemm_any(R.xa.data_ptr(), f32, W, self.arena.ptr(w + "mlp.router"), f32, W, n, e.experts, W,
                                         R.router.data_ptr(), e.experts, st))
-            _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, n, e.experts, e.top, mode, *route))
+            _lib.check(lib.prl_moe_route(R.router.data_ptr(), e.experts, bias, n, e.experts, e.top, mode, *route))
         tiles = int(lib.prl_moe_max_tiles(pairs, e.experts))
         table = (R.perm.data_ptr(), R.moe_meta.data_ptr(), R.moe_tiles.data_ptr(), tiles)
         _lib.check(lib.prl_moe_gemm(R.xa.data_ptr(), f32, W, n, self.arena.ptr(w + "mlp.experts.gate_up"), f32,
@@ -1177,6 +1451,137 @@ class HybridEngine(EngineCore):
                     gain1=vec[w + "mix.right.out"], s1=L.right_scale,
                     post_gain=vec[w + "norm1b"] if L.sandwich else vec[w + "norm1"], next_gain=self._next_gain(i, True))
 
+    # ---- the 'post_ln' block: every sublayer is normed after the sum, x <- norm(skip_scale x + f(x)), f reads x ----------
+    def _postln_close(self, R, n, w, q, y0, k0, s0=1.0, y1=None, k1=1, s1=1.0, bias=None) -> None:
+        """x <- rmsnorm(skip_scale x + s0 y0 + s1 y1 + bias) * norm<q>, and its copy in the operand type."""
+        cfg, ptr = self.cfg, (lambda t: None if t is None else t.data_ptr())
+        _lib.check(self.lib.prl_postln_close(y0.data_ptr(), cfg.width, s0, k0, ptr(y1), cfg.width, s1, k1, ptr(bias),
+                                             cfg.skip_scale, self.vec[w + "norm" + q].data_ptr(), cfg.eps, n, cfg.width,
+                                             R.x.data_ptr(), R.xa.data_ptr(), int(self.f32), self._st))
+
+    def _postln_layers(self, R, n, ns, max_q, row_pos, seg_pos0, trace=None) -> None:
+        cfg, vec = self.cfg, self.vec
+        segs = (R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr(), ns)
+        for i, L in enumerate(cfg.layers):
+            w = f"l{L.weights_of}."
+            if L.kind == "attention":
+                k0 = self._window_attn_mixer(R, n, i, L, w, segs, max_q, row_pos, seg_pos0)
+                self._postln_close(R, n, w, "1", R.y0, k0, bias=vec[w + "mix.o.b"] if L.attn.o_bias else None)
+            elif L.kind == "latent_attention":
+                k0 = self._latent_direct_mixer(R, n, i, L, w, segs, max_q, row_pos, seg_pos0)
+                self._postln_close(R, n, w, "1", R.y0, k0)
+            else:
+                k0, k1 = self._sigmoid_delta_mixer(R, n, i, L, w, segs, max_q, row_pos, seg_pos0)
+                self._postln_close(R, n, w, "1", R.y0, k0, s0=L.left_scale, y1=R.y1, k1=k1, s1=L.right_scale)
+            if L.mlp is not None:
+                y = self._routed_ff(R, n, w, L.mlp.moe, L.mlp.beta)
+                self._postln_close(R, n, w, "2", y, L.mlp.moe.top)
+            if trace is not None:
+                trace.append(R.x[:n * cfg.width].view(n, cfg.width).clone())
+
+    def _window_attn_mixer(self, R, n, i, L, w, segs, max_q, row_pos, seg_pos0) -> int:
+        """Softmax attention with biased projections, per-head norms with a shared gain, scaled rotate-half rotary,
+        unit-RMS values blended with an earlier layer's, a sliding window, a sink logit and one gate per head, from ONE
+        projection [q | k | v | g].  Returns the number of split-K slices of the output projection left in R.y0."""
+        a, lib, st, vec, f32, W = L.attn, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        seg_start, seg_len, seg_slot, ns = segs
+        nq, nk, nv, no = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim, a.heads * a.vdim
+        ld, P = nq + nk + nv + (a.heads if a.gate else 0), R.P.data_ptr()
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        qb = vec[w + "mix.qk.b"].data_ptr() if a.bias else None
+        gain = (vec[w + "mix.q.norm"].data_ptr(), vec[w + "mix.k.norm"].data_ptr()) if a.head_gain else (None, None)
+        _lib.check(lib.prl_attn_front(P, ld, 0, nq, nq + nk, n, a.heads, a.kv_heads, a.dim, a.vdim, qb,
+                                      qb + 4 * nq if a.bias else None, vec[w + "mix.v.b"].data_ptr() if a.v_bias else None,
+                                      int(a.head_norm), *gain, a.dim, self.cfg.eps, a.rot_dims, self.rot_freq[i].data_ptr(),
+                                      self.rot_mag[i], int(a.v_norm), a.v_mix,
+                                      vec[w + "mix.vmix"].data_ptr() if a.v_mix else None,
+                                      R.vfirst.data_ptr() if a.v_mix else None, row_pos.data_ptr(), R.row_slot.data_ptr(),
+                                      self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, R.q.data_ptr(),
+                                      self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32, st))
+        sink = vec[w + "mix.sink"].data_ptr() if a.sink else None
+        gated = a.gate and a.gate_per_head
+        _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), a.vdim, f32,
+                                         self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
+                                         seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                                         a.window, 0, a.softcap, sink, 0 if gated else 1,
+                                         R.o.data_ptr() if gated else R.ya.data_ptr(), st))
+        if gated:
+            _lib.check(lib.prl_gate_heads(R.o.data_ptr(), 1, no, P + 4 * (nq + nk + nv), ld, n, a.heads, a.vdim, R.ya.data_ptr(),
+                                          f32, st))
+        return self._mm(R.ya, no, w + "mix.o", W, R.y0, n, split=True)
+
+    def _latent_direct_mixer(self, R, n, i, L, w, segs, max_q, row_pos, seg_pos0) -> int:
+        """Latent attention whose query comes straight from the layer's input: ONE projection [q | dkv | g].  As in
+        _latent_mixer the key expansion is absorbed into the query and the value expansion follows the attention, so
+        the cache holds [latent | rotated shared key part] per token.  Buffers: yb = the heads' unrotated query parts,
+        later the gated values (operand type); q = the attention query [n][H][kv_rank + rot_dim]; ya = the attention
+        output over the latent (operand type); o = scratch of the per-head products, then the expanded values (fp32)."""
+        a, lib, st, vec, f32, W = L.latent, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        seg_start, seg_len, seg_slot, ns = segs
+        H, rk, dr, dv = a.heads, a.kv_rank, a.rot_dim, a.vdim
+        hq, kd = H * (a.dim + dr), rk + dr
+        ld, P = hq + kd + (H * dv if a.gate else 0), R.P.data_ptr()
+        il = int(a.interleaved)
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        _lib.check(lib.prl_latent_prep(P, ld, 0, 0, hq, rk, dr, self.rot_freq[i].data_ptr(), None,
+                                       vec[w + "mix.dkv.norm"].data_ptr(), self.cfg.eps, row_pos.data_ptr(),
+                                       R.row_slot.data_ptr(), self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, n, il,
+                                       None, self.lat_pool[i].data_ptr(), f32, st))
+        _lib.check(lib.prl_latent_query(P, ld, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(), row_pos.data_ptr(), il,
+                                        R.yb.data_ptr(), R.q.data_ptr(), f32, st))
+        self._mm_heads(R.yb, a.dim, self.uk_t[L.weights_of].data_ptr(), rk * a.dim, n, rk, R.o, H, R.q, kd)
+        pool = self.lat_pool[i].data_ptr()
+        _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
+                                         PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
+                                         rk, a.scale, a.window, 0, 0.0, None, 1, R.ya.data_ptr(), st))
+        if a.gate:       # v[h] = W_uv,h o_lat[h] in fp32, times sigmoid(g) element by element
+            self._mm_heads(R.ya, rk, self.arena.ptr(w + "mix.uv"), dv * rk, n, dv, R.o, H, None, 0, store=False)
+            _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, H * dv, P + 4 * (hq + kd), ld, None, 1, H * dv, n, H * dv, 1, 0, 0,
+                                         self.cfg.eps, R.yb.data_ptr(), f32, st))
+        else:
+            self._mm_heads(R.ya, rk, self.arena.ptr(w + "mix.uv"), dv * rk, n, dv, R.o, H, R.yb, dv)
+        return self._mm(R.yb, H * dv, w + "mix.o", W, R.y0, n, split=True)
+
+    def _sigmoid_delta_mixer(self, R, n, i, L, w, segs, max_q, row_pos, seg_pos0):
+        """Attention without a softmax beside the gated delta rule, both from ONE projection
+        [q | k | v || q | k | v | b | a | g].  Returns the split-K slice counts of the two output projections
+        (R.y0, R.y1); the caller's closing kernel adds them with the layer's two scales."""
+        a, g, lib, st, vec, f32, W = L.attn, L.gdelta, self.lib, self._st, self.vec, int(self.f32), self.cfg.width
+        seg_start, seg_len, seg_slot, ns = segs
+        nq, nk, nv, no = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim, a.heads * a.vdim
+        left = nq + nk + nv
+        ld, P = left + g.in_rows, R.P.data_ptr()
+        self._mm(R.xa, W, w + "mix.in", ld, R.P, n)
+        # -- left: one RMS norm over all heads of q (and of k), no rotation; the temperature is folded into the score scale
+        _lib.check(lib.prl_qk_norm_rope_cache(P, ld, 0, nq, nq + nk, n, a.heads, a.kv_heads, a.dim, a.vdim, 0,
+                                              self.rot_freq[i].data_ptr(), vec[w + "mix.left.q.norm"].data_ptr(),
+                                              vec[w + "mix.left.k.norm"].data_ptr(), self.cfg.eps, row_pos.data_ptr(),
+                                              R.row_slot.data_ptr(), self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE,
+                                              R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32, st))
+        _lib.check(lib.prl_attn_sigmoid(R.q.data_ptr(), self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32,
+                                        self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
+                                        seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                                        a.softcap, a.q_temp[0], a.q_temp[1], vec[w + "mix.left.pb"].data_ptr(),
+                                        vec[w + "mix.left.talk"].data_ptr() if a.talking else None, 1, R.ya.data_ptr(), st))
+        k0 = self._mm(R.ya, no, w + "mix.left.o", W, R.y0, n, split=True)
+        # -- right: convolutions + SiLU over [q | k | v], then the scan
+        gq, gv, ch = g.kv_heads * g.dim, g.heads * g.vdim, g.conv_channels
+        _lib.check(lib.prl_conv_silu(P, ld, left, n, ch, g.conv, vec[w + "mix.right.conv"].data_ptr(), self.zero_bias.data_ptr(),
+                                     R.row_slot.data_ptr(), R.row_back.data_ptr(), self.conv_state[i].data_ptr(),
+                                     R.aux.data_ptr(), st))
+        _lib.check(lib.prl_conv_state_update(P, ld, left, ch, g.conv, seg_start, seg_len, seg_slot, ns,
+                                             self.conv_state[i].data_ptr(), st))
+        _lib.check(lib.prl_gated_delta_scan(R.aux.data_ptr(), ch, 0, gq, 2 * gq, P, ld, left + ch, left + ch + g.heads,
+                                            vec[w + "mix.right.A_log"].data_ptr(), vec[w + "mix.right.dt_bias"].data_ptr(),
+                                            g.unit_eps, g.heads, g.kv_heads, g.dim, g.vdim, n, R.dprep.data_ptr(), seg_start,
+                                            seg_len, seg_slot, ns, max_q, self.delta_state[i].data_ptr(), R.o.data_ptr(), gv,
+                                            st))
+        _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, gv, P + 4 * (left + ch + 2 * g.heads), ld,
+                                     vec[w + "mix.right.norm"].data_ptr(), g.vdim, g.vdim, n, gv, 0, 0, 1, self.cfg.eps,
+                                     R.yb.data_ptr(), f32, st))
+        k1 = self._mm(R.yb, gv, w + "mix.right.o", W, R.y1, n, split=True)
+        return k0, k1
+
     # ---- the multi-stream program: latent attention and delta-rule layers ------------------------------------------------
     def _stream_weights(self, i: int, q: str):
         """(read weights, write weights, mixing matrix) of sublayer q of run i; a layer without them sums plainly."""
@@ -1253,11 +1658,11 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_latent_prep(P, ld, 0, a.q_rank, a.q_rank, rk, dr, self.rot_freq[i].data_ptr(),
                                        vec[w + "mix.dq.norm"].data_ptr(), vec[w + "mix.dkv.norm"].data_ptr(), self.cfg.eps,
                                        row_pos.data_ptr(), R.row_slot.data_ptr(), self.block_table.data_ptr(), self.max_blocks,
-                                       PAGE_SIZE, n, R.ya.data_ptr(), self.lat_pool[i].data_ptr(), f32, st))
+                                       PAGE_SIZE, n, 0, R.ya.data_ptr(), self.lat_pool[i].data_ptr(), f32, st))
         hq = H * (a.dim + dr)
         self._mm(R.ya, a.q_rank, w + "mix.uq", hq, R.aux, n)
         _lib.check(lib.prl_latent_query(R.aux.data_ptr(), hq, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(),
-                                        row_pos.data_ptr(), R.yb.data_ptr(), R.q.data_ptr(), f32, st))
+                                        row_pos.data_ptr(), 0, R.yb.data_ptr(), R.q.data_ptr(), f32, st))
         # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers, into the attention query
         self._mm_heads(R.yb, a.dim, self.uk_t[L.weights_of].data_ptr(), rk * a.dim, n, rk, R.o, H, R.q, kd)
         pool = self.lat_pool[i].data_ptr()
@@ -1289,7 +1694,7 @@ class HybridEngine(EngineCore):
                                       torch.tensor(tiles, **i32).reshape(-1), len(tiles))
         return self._head_tables[key]
 
-    def _mm_heads(self, src, K, w_ptr, w_step, n, N, tmp, heads, dst, dst_step) -> None:
+    def _mm_heads(self, src, K, w_ptr, w_step, n, N, tmp, heads, dst, dst_step, store: bool = True) -> None:
         """dst[t][h][:N] (operand type, rows dst_step apart) = src[t][h][:K] @ W_h[N, K]^T for every token t and head h
         (W_h = w_ptr + h * w_step elements, rows K apart): ONE grouped GEMM over the heads (tensor cores for bf16), the
         routed feed-forward's kernel with the head in the expert's place, into the fp32 buffer `tmp`, and a cast."""
@@ -1297,7 +1702,8 @@ class HybridEngine(EngineCore):
         perm, meta, tiles, n_tiles = self._head_table(n, heads)
         _lib.check(lib.prl_moe_gemm(src.data_ptr(), f32, K, n * heads, w_ptr, f32, w_step, K, perm.data_ptr(), meta.data_ptr(),
                                     tiles.data_ptr(), n_tiles, N, K, tmp.data_ptr(), N, 1, st))
-        _lib.check(lib.prl_store_groups(tmp.data_ptr(), heads * N, n, heads, N, dst.data_ptr(), dst_step, f32, st))
+        if store:                                        # else the caller consumes the fp32 rows [n][heads * N] in tmp
+            _lib.check(lib.prl_store_groups(tmp.data_ptr(), heads * N, n, heads, N, dst.data_ptr(), dst_step, f32, st))
 
     def _delta_mixer(self, R, n, i, L, w, segs, max_q=0):
         """Delta-rule memory: one projection [r | k | v | g | a | w1 | gate]; the decay logits come through the tanh
@@ -1365,7 +1771,7 @@ class HybridEngine(EngineCore):
         self._embed(R, B, self.tokens, self.positions)
         self._layers(R, B, B, 1, self.positions, self.positions, decode=True)
         self._final_norm(R, None, B)
-        self._mm(R.xa, cfg.width, "head", cfg.vocab_size, self.logits, B)
+        self._mm(R.xa, cfg.width, self.head_name, cfg.vocab_size, self.logits, B)
 
     # ---- a packed batch of prompt portions (prefill chunks, token streams) --------------------------------------------
     def _forward_rows(self, segs, want_rows, trace=None):
@@ -1415,5 +1821,5 @@ class HybridEngine(EngineCore):
         R.want[:nw].copy_(torch.tensor(want_rows, dtype=i32), non_blocking=True)
         self._final_norm(R, R.want.data_ptr(), nw)
         out = torch.empty(nw, cfg.vocab_size, dtype=torch.float32, device=self.dev)
-        self._mm(R.xa, cfg.width, "head", cfg.vocab_size, out, nw)
+        self._mm(R.xa, cfg.width, self.head_name, cfg.vocab_size, out, nw)
         return out

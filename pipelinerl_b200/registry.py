@@ -113,6 +113,11 @@ def _pametar_config(config: dict, shapes: dict):
     return HybridConfig.from_pametar(config, shapes)
 
 
+def _kolotar_config(config: dict, shapes: dict):
+    from .hybrid import HybridConfig
+    return HybridConfig.from_kolotar(config, shapes)
+
+
 def _hybrid_engine():
     from .hybrid import HybridEngine
     return HybridEngine
@@ -122,6 +127,7 @@ register(Family("Qwen2ForCausalLM", _qwen2_config, _qwen2_engine, (torch.bfloat1
 register(Family("Povurax", _povurax_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 register(Family("Belelorn", _belelorn_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 register(Family("Pametar", _pametar_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
+register(Family("Kolotar", _kolotar_config, _hybrid_engine, (torch.bfloat16, torch.float32)))
 
 
 def parse_dtype(name: str) -> torch.dtype:
