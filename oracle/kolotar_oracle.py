@@ -327,3 +327,71 @@ def forward(cfg: dict, weights: dict, tokens, round_inputs: bool = False, margin
     xn = rms_norm(x, c.w["final.norm"], eps)
     logits = (_bf16(xn) if round_inputs else xn) @ c.w["embed"].T
     return logits, torch.stack(trace) if trace else torch.zeros(0, tok.numel(), x.shape[-1], dtype=F64)
+
+
+# ---- random checkpoints for the tests ---------------------------------------------------------------------------------
+def tensor_shapes(cfg: dict) -> dict:
+    """{tensor name: shape} of a checkpoint of this config."""
+    W, out = int(cfg["width"]), {"embed": (int(cfg["vocab"]), int(cfg["width"])), "final.norm": (int(cfg["width"]),)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.mix.", L["mixer"]
+        if L["type"] == "attention":
+            H, G, d, dv = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
+            for name, rows in (("q", H * d), ("k", G * d), ("v", G * dv), ("o", W)):
+                out[p + name] = (rows, W if name != "o" else H * dv)
+                out[p + name + ".b"] = (rows,)
+            out.update({p + "q.norm": (d,), p + "k.norm": (d,), p + "vmix": (), p + "sink": (H,), p + "g": (H, W)})
+        elif L["type"] == "latent_attention":
+            H, d, dr, dv, r = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
+            out.update({p + "q": (H * (d + dr), W), p + "dkv": (r + dr, W), p + "dkv.norm": (r,), p + "uk": (H * d, r),
+                        p + "uv": (H * dv, r), p + "g": (H * dv, W), p + "o": (W, H * dv)})
+        else:
+            a, r = m["left"], m["right"]
+            H, G, d, dv = int(a["heads"]), int(a.get("kv_heads", a["heads"])), int(a["dim"]), int(a["vdim"])
+            out.update({p + "left.q": (H * d, W), p + "left.k": (G * d, W), p + "left.v": (G * dv, W), p + "left.q.norm": (H * d,),
+                        p + "left.k.norm": (G * d,), p + "left.pb": (H,), p + "left.talk": (H, H), p + "left.o": (W, H * dv)})
+            Hv, Gk, dk, dvr, taps = int(r["heads"]), int(r.get("kv_heads", r["heads"])), int(r["dim"]), int(r["vdim"]), int(r["conv"])
+            out.update({p + "right.q": (Gk * dk, W), p + "right.q.conv": (Gk * dk, taps), p + "right.k": (Gk * dk, W),
+                        p + "right.k.conv": (Gk * dk, taps), p + "right.v": (Hv * dvr, W), p + "right.v.conv": (Hv * dvr, taps),
+                        p + "right.b": (Hv, W), p + "right.A_log": (Hv,), p + "right.norm": (dvr,), p + "right.a": (Hv, W),
+                        p + "right.dt_bias": (Hv,), p + "right.g": (Hv * dvr, W), p + "right.o": (W, Hv * dvr)})
+        out[f"l{i}.norm1"] = (W,)
+        f = L.get("mlp")
+        if f is not None:
+            E, ff = int(f["router"]["experts"]), int(f["expert"]["ff"])
+            for e in range(E):
+                out.update({f"l{i}.mlp.e{e}.gate": (ff, W), f"l{i}.mlp.e{e}.up": (ff, W), f"l{i}.mlp.e{e}.down": (W, ff)})
+            out.update({f"l{i}.mlp.router": (E, W), f"l{i}.mlp.router.b": (E,), f"l{i}.norm2": (W,)})
+    return out
+
+
+def random_weights(cfg: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
+    """Random tensors rounded to `dtype`, so that the engine and the oracle see the same numbers.  Matrices have unit
+    row gain, gains are spread around one, router rows are scaled so that the choice is rarely a close call."""
+    g = torch.Generator().manual_seed(seed)
+    wt = {}
+    for name, shape in tensor_shapes(cfg).items():
+        leaf = name.split(".")[-1]
+        rnd = lambda std=1.0: torch.randn(shape, generator=g) * std
+        if leaf in ("norm1", "norm2", "norm") or name == "final.norm":
+            t = 1.0 + rnd(0.2)
+        elif name == "embed":
+            t = rnd(0.7)
+        elif leaf == "vmix":
+            t = 0.2 + 0.6 * torch.rand(shape, generator=g)
+        elif leaf == "talk":
+            t = torch.eye(shape[0]) + rnd(0.3)
+        elif leaf == "A_log":
+            t = torch.log(0.05 + 0.5 * torch.rand(shape, generator=g))
+        elif leaf in ("sink", "pb", "dt_bias"):
+            t = rnd(1.0)
+        elif leaf == "b" and len(shape) == 1:
+            t = rnd(0.3)
+        elif leaf == "conv":
+            t = rnd(0.6)
+        elif leaf == "router":
+            t = rnd(4.0 / math.sqrt(shape[-1]))
+        else:
+            t = rnd(1.0 / math.sqrt(shape[-1]))
+        wt[name] = t.to(dtype).to(F64)
+    return wt

@@ -61,6 +61,7 @@ class AttnSpec:
     rot_scaling: tuple | None = None   # YaRN: (factor, original length, fast turns, slow turns)
     v_norm: bool = False        # every value head divided by its root mean square (no gain) before it is cached
     v_mix: int = 0              # 1: this layer's values are kept for later layers; 2: v <- (1 - l) v + l v_first, l = `vmix`
+    v_mix_tensor: bool = False  # the checkpoint has a `vmix` scalar for this layer (used only when v_mix == 2)
     sink: bool = False          # a learned logit per head in the softmax denominator (no key, no value)
     weights: str = "softmax"    # "sigmoid": weight = sigmoid(score + pb[h]) for every visible key, not normalised
     q_temp: tuple = (0.0, 1.0)  # (coef, every): q times 1 + coef * ln(floor((pos + 1) / every) + 1)
@@ -437,7 +438,8 @@ class HybridConfig:
                                 bias=has("mix.q.b"), v_bias=has("mix.v.b"), o_bias=has("mix.o.b"), gate=has("mix.g"),
                                 gate_per_head=True, rot_half=True,
                                 rot_scaling=(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None,
-                                v_norm=True, v_mix=mix, sink=has("mix.sink"))
+                                v_norm=True, v_mix=mix, v_mix_tensor=has("mix.vmix") if shapes else mix == 2,
+                                sink=has("mix.sink"))
                 layers.append(LayerSpec("attention", i, attn=attn, mlp=mlp))
             elif L["type"] == "latent_attention":
                 rot = m.get("rot") or {}
@@ -666,7 +668,7 @@ class HybridConfig:
                 one("mix.v.b", (nv,))
             if a.head_gain:
                 one("mix.q.norm", (a.dim,)); one("mix.k.norm", (a.dim,))
-            if a.v_mix:
+            if a.v_mix_tensor or a.v_mix == 2:
                 one("mix.vmix", (1,))
             if a.sink:
                 one("mix.sink", (a.heads,))
@@ -1494,7 +1496,7 @@ class HybridEngine(EngineCore):
                                       qb + 4 * nq if a.bias else None, vec[w + "mix.v.b"].data_ptr() if a.v_bias else None,
                                       int(a.head_norm), *gain, a.dim, self.cfg.eps, a.rot_dims, self.rot_freq[i].data_ptr(),
                                       self.rot_mag[i], int(a.v_norm), a.v_mix,
-                                      vec[w + "mix.vmix"].data_ptr() if a.v_mix else None,
+                                      vec[w + "mix.vmix"].data_ptr() if a.v_mix == 2 else None,
                                       R.vfirst.data_ptr() if a.v_mix else None, row_pos.data_ptr(), R.row_slot.data_ptr(),
                                       self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, R.q.data_ptr(),
                                       self.k_pool[i].data_ptr(), self.v_pool[i].data_ptr(), f32, st))
