@@ -57,12 +57,14 @@ def parse():
     ap.add_argument("--no-rollout", action="store_true", help="N = 1: skip the full-rollout run through the plugin API")
     ap.add_argument("--rollout-tokens", type=int, default=8192, help="max_tokens of the full-rollout component")
     ap.add_argument("--splits", default="", help="learner counts of the split runs, e.g. '2,4' (default: by N)")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "hybrid", "belelorn", "pametar"],
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "hybrid", "belelorn", "pametar", "kolotar"],
                     help="hybrid: prefill / decode throughput of the hybrid decoder family (GLA, attention + state-space "
                          "layers) beside the Qwen2 engine at equal sizes, and its kernels against their rooflines "
                          "(tools/hybrid_bench.py); belelorn: the same for the Belelorn design (mLSTM, windowed attention "
                          "beside lightning attention, routed feed-forwards) beside the Povurax hybrid and Qwen2; pametar: the "
-                         "Pametar design (latent attention, delta-rule memory, residual streams) beside Belelorn and Qwen2; "
+                         "Pametar design (latent attention, delta-rule memory, residual streams) beside Belelorn and Qwen2; kolotar: "
+                         "the Kolotar design (windowed attention with a sink, latent attention, attention without a softmax "
+                         "beside the gated delta rule, norms after the sum) beside Pametar and Qwen2; "
                          "the default workload and its JSON line are unchanged")
     ap.add_argument("--sizes", default="w2048,w4096", help="--arch hybrid: model sizes to compare")
     return ap.parse_args()
@@ -619,8 +621,9 @@ def run_hybrid(args):
     sampler = ClockSampler(0)
     sampler.start()
     sizes = args.sizes.split(",")
-    which = args.arch if args.arch in ("belelorn", "pametar") else "hybrid"
-    runner = {"belelorn": hybrid_bench.run_belelorn, "pametar": hybrid_bench.run_pametar}.get(which, hybrid_bench.run)
+    which = args.arch if args.arch in ("belelorn", "pametar", "kolotar") else "hybrid"
+    runner = {"belelorn": hybrid_bench.run_belelorn, "pametar": hybrid_bench.run_pametar,
+              "kolotar": hybrid_bench.run_kolotar}.get(which, hybrid_bench.run)
     res = runner(sizes, prompt=4096, context=2048, batch=32, steps=args.steps, warm=max(3, args.warmup))
     clocks = sampler.stop()
     first = res[sizes[0]][which]
@@ -634,7 +637,7 @@ def run_hybrid(args):
 
 if __name__ == "__main__":
     a = parse()
-    if a.arch in ("hybrid", "belelorn", "pametar"):
+    if a.arch in ("hybrid", "belelorn", "pametar", "kolotar"):
         run_hybrid(a)
     elif a.impl == "reference":
         run_reference(a)

@@ -758,7 +758,8 @@ size_t prl_attn_latent_workspace_bytes(int32_t n_seg, int32_t H, int32_t rank);
  * tokens spreads each sequence's keys over several CTAs whose shares a second launch merges */
 int prl_attn_latent(const void* q, const void* pool, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
                     const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_pos0, const int32_t* seg_slot,
-                    int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank, float scale, const float* sink,
+                    int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank, float scale,
+                    int32_t window /* > 0: a query sees its last `window` positions only */, const float* sink,
                     void* out, void* ws, size_t ws_bytes, prl_stream_t stream);
 /* query latent cq = rmsnorm(P[off_q : off_q + q_rank]) * q_gain (operand type) and the latent cache row
  * [rmsnorm(P[off_kv : +rank]) * kv_gain | rotate(P[off_kv + rank : +rot], pos)] -> pool[page][page_size][rank + rot];

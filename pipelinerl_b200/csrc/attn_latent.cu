@@ -71,10 +71,11 @@ struct Acc {
 };
 
 // One key tile (32 keys starting at absolute key k0, rows Ks[key][ld]) against the warp's 16 stacked query rows Qs[16][ld].
-// pos[i]: the position of the token of row g + 8 i (keys <= pos are visible; -1 hides everything: a padding row).
+// pos[i]: the position of the token of row g + 8 i (keys lo[i] .. pos[i] are visible; pos -1 hides everything: a padding
+// row; lo is 0 without a sliding window, else pos - window + 1).
 template <int NV>
 __device__ __forceinline__ void tile_step(Acc<NV>& a, const bf16* Qs, const bf16* Ks, int ld, int kd, int rank, int k0,
-                                          const int (&pos)[2], float scale, int lane) {
+                                          const int (&pos)[2], const int (&lo)[2], float scale, int lane) {
   float s[4][4];
 #pragma unroll
   for (int j = 0; j < 4; ++j)
@@ -100,7 +101,7 @@ __device__ __forceinline__ void tile_step(Acc<NV>& a, const bf16* Qs, const bf16
     for (int e = 0; e < 4; ++e) {
       const int key = k0 + 8 * j + t2 + (e & 1);
       const int i = e >> 1;
-      const float v = key <= pos[i] ? s[j][e] * scale : -INFINITY;
+      const float v = (key <= pos[i] && key >= lo[i]) ? s[j][e] * scale : -INFINITY;
       s[j][e] = v;
       mx[i] = fmaxf(mx[i], v);
     }
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) attn_latent_rows_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int page_size, const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
     const int32_t* __restrict__ seg_pos0, const int32_t* __restrict__ seg_slot, int H, int kd, int rank, float scale,
-    const float* __restrict__ sink, bf16* __restrict__ out) {
+    int window, const float* __restrict__ sink, bf16* __restrict__ out) {
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int seg = blockIdx.y;
@@ -223,21 +224,31 @@ __global__ void __launch_bounds__(kRowWarps * 32) attn_latent_rows_kernel(
   }
   const int last_key = pos0 + (cta_m0 + m_here - 1) / H;      // the CTA's last token sees keys 0 .. last_key
   const int n_tiles = last_key / kKeys + 1;
-  stage_keys(Kb0, ld, pool, bt, page_size, kd, 0, last_key, tid, blockDim.x);
+  // with a sliding window the CTA's first token hides the keys before first_key: whole tiles before it are skipped (the
+  // others keep their absolute place, so the order of summation does not depend on the cutting of the prompt)
+  const int first_key = window > 0 ? max(pos0 + cta_m0 / H - window + 1, 0) : 0;
+  const int t_first = first_key / kKeys;
+  stage_keys(Kb0, ld, pool, bt, page_size, kd, t_first * kKeys, last_key, tid, blockDim.x);
   cp_commit();
   const int m0 = cta_m0 + warp * 16, g = lane >> 2;
-  int pos[2];
+  int pos[2], lo[2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) pos[i] = (m0 + g + 8 * i) < m_total ? pos0 + (m0 + g + 8 * i) / H : -1;
+  for (int i = 0; i < 2; ++i) {
+    pos[i] = (m0 + g + 8 * i) < m_total ? pos0 + (m0 + g + 8 * i) / H : -1;
+    lo[i] = window > 0 ? pos[i] - window + 1 : 0;
+  }
   const int warp_last = m0 < m_total ? pos0 + min(m0 + 15, m_total - 1) / H : -1;      // warp-uniform: the warp's last visible key
+  const int warp_first = (window > 0 && m0 < m_total) ? pos0 + m0 / H - window + 1 : 0;  // ... and its first
   Acc<NV> acc;
   acc.init();
-  for (int t = 0; t < n_tiles; ++t) {
-    if (t + 1 < n_tiles) stage_keys(Kb0 + ((t + 1) & 1) * kb_step, ld, pool, bt, page_size, kd, (t + 1) * kKeys, last_key, tid, blockDim.x);
+  for (int t = t_first; t < n_tiles; ++t) {
+    const int b = (t - t_first) & 1;
+    if (t + 1 < n_tiles) stage_keys(Kb0 + (b ^ 1) * kb_step, ld, pool, bt, page_size, kd, (t + 1) * kKeys, last_key, tid, blockDim.x);
     cp_commit();
     cp_wait<1>();
     __syncthreads();
-    if (t * kKeys <= warp_last) tile_step<NV>(acc, Qs + warp * 16 * ld, Kb0 + (t & 1) * kb_step, ld, kd, rank, t * kKeys, pos, scale, lane);
+    if (t * kKeys <= warp_last && (t + 1) * kKeys > warp_first)
+      tile_step<NV>(acc, Qs + warp * 16 * ld, Kb0 + b * kb_step, ld, kd, rank, t * kKeys, pos, lo, scale, lane);
     __syncthreads();
   }
   if (m0 < m_total) finish_rows<NV>(acc, sink, H, rank, m0, m_total, row0, out, lane);
@@ -248,7 +259,7 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ pool, const int32_t* __restrict__ block_table, int max_blocks,
     int page_size, const int32_t* __restrict__ seg_start, const int32_t* __restrict__ seg_len,
     const int32_t* __restrict__ seg_pos0, const int32_t* __restrict__ seg_slot, int H, int kd, int rank, float scale,
-    const float* __restrict__ sink, bf16* __restrict__ out, int splits, float* __restrict__ ws) {
+    int window, const float* __restrict__ sink, bf16* __restrict__ out, int splits, float* __restrict__ ws) {
   pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int seg = blockIdx.y, z = blockIdx.z;
@@ -268,19 +279,23 @@ __global__ void __launch_bounds__(kSplitWarps * 32) attn_latent_split_kernel(
         r < m_here ? *reinterpret_cast<const uint4*>(q + (row0 * H + m0 + r) * kd + c * 8) : make_uint4(0u, 0u, 0u, 0u);
   }
   __syncthreads();
-  int pos[2];
+  int pos[2], lo[2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) pos[i] = (m0 + g + 8 * i) < m_total ? pos_tok : -1;
+  for (int i = 0; i < 2; ++i) {
+    pos[i] = (m0 + g + 8 * i) < m_total ? pos_tok : -1;
+    lo[i] = window > 0 ? pos_tok - window + 1 : 0;
+  }
   const int n_tiles = pos_tok / kKeys + 1;
+  const int t_first = window > 0 ? max(pos_tok - window + 1, 0) / kKeys : 0;     // tiles before the window are skipped
   Acc<NV> acc;
   acc.init();
-  for (int t = z * kSplitWarps + warp; t < n_tiles; t += kSplitWarps * splits) {     // CTA z of `splits` takes every splits-th turn
+  for (int t = t_first + z * kSplitWarps + warp; t < n_tiles; t += kSplitWarps * splits) {     // CTA z of `splits` takes every splits-th turn
     __syncwarp();
     stage_keys(Ks, ld, pool, bt, page_size, kd, t * kKeys, pos_tok, lane, 32);
     cp_commit();
     cp_wait<0>();
     __syncwarp();
-    tile_step<NV>(acc, Qs, Ks, ld, kd, rank, t * kKeys, pos, scale, lane);
+    tile_step<NV>(acc, Qs, Ks, ld, kd, rank, t * kKeys, pos, lo, scale, lane);
   }
   __syncthreads();                                                     // the key tiles are dead: their space holds the partials
   // partial of warp w: [16 rows][rank + 2] fp32 = o | m | l
@@ -390,9 +405,10 @@ extern "C" size_t prl_attn_latent_workspace_bytes(int32_t n_seg, int32_t H, int3
 extern "C" int prl_attn_latent(const void* q, const void* pool, const int32_t* block_table, int32_t max_blocks, int32_t page_size,
                                const int32_t* seg_start, const int32_t* seg_len, const int32_t* seg_pos0,
                                const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H, int32_t kd, int32_t rank,
-                               float scale, const float* sink, void* out, void* ws, size_t ws_bytes, prl_stream_t stream) {
+                               float scale, int32_t window, const float* sink, void* out, void* ws, size_t ws_bytes,
+                               prl_stream_t stream) {
   PRL_CHECK_ARG(q && pool && block_table && seg_start && seg_len && seg_pos0 && seg_slot && out, "prl_attn_latent: NULL argument");
-  PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && max_blocks >= 1 && prl_attn_latent_fits(kd, rank, page_size),
+  PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && max_blocks >= 1 && window >= 0 && prl_attn_latent_fits(kd, rank, page_size),
                 "prl_attn_latent: geometry kd=%d rank=%d page=%d is not built (see prl_attn_latent_fits)", kd, rank, page_size);
   PRL_CHECK_ARG(((uintptr_t)q & 15) == 0 && ((uintptr_t)pool & 15) == 0 && ((uintptr_t)out & 3) == 0, "prl_attn_latent: misaligned buffer");
   cudaStream_t st = (cudaStream_t)stream;
@@ -403,13 +419,13 @@ extern "C" int prl_attn_latent(const void* q, const void* pool, const int32_t* b
   do {                                                                                                                    \
     if (rank <= 64) {                                                                                                     \
       PRL_CUDA(ensure_smem(KERNEL<8>, (int)(SMEM), ATTR[0]));                                                             \
-      PRL_CUDA(launch_pdl(KERNEL<8>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
+      PRL_CUDA(launch_pdl(KERNEL<8>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, window, sink, oo EXTRA)); \
     } else if (rank <= 128) {                                                                                             \
       PRL_CUDA(ensure_smem(KERNEL<16>, (int)(SMEM), ATTR[1]));                                                            \
-      PRL_CUDA(launch_pdl(KERNEL<16>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
+      PRL_CUDA(launch_pdl(KERNEL<16>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, window, sink, oo EXTRA)); \
     } else {                                                                                                              \
       PRL_CUDA(ensure_smem(KERNEL<32>, (int)(SMEM), ATTR[2]));                                                            \
-      PRL_CUDA(launch_pdl(KERNEL<32>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, sink, oo EXTRA)); \
+      PRL_CUDA(launch_pdl(KERNEL<32>, GRID, dim3(THREADS), (size_t)(SMEM), st, qq, pp, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, H, kd, rank, scale, window, sink, oo EXTRA)); \
     }                                                                                                                     \
   } while (0)
   if (max_q == 1) {

@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
                                                        int max_blocks, int page_size, const int32_t* __restrict__ seg_start,
                                                        const int32_t* __restrict__ seg_len, const int32_t* __restrict__ seg_pos0,
                                                        const int32_t* __restrict__ seg_slot, int H, int G, float scale,
-                                                       int window, int keep_first, float softcap, void* __restrict__ out_v) {
+                                                       int window, int keep_first, float softcap, const float* __restrict__ sink,
+                                                       void* __restrict__ out_v) {
   pdl_wait();
   constexpr int LD = D + kPadH;            // halves per staged row: (D + 8) * 2 bytes, a multiple of 16, odd in 16-byte units
   constexpr int CH = D / 8;                // 16-byte chunks per row
@@ -193,7 +194,12 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
 #pragma unroll
   for (int u = 0; u < 2; ++u) {
     if (my_pos[u] < 0) continue;
-    const float inv = 1.f / l[u];
+    float inv = 1.f / l[u];
+    if (sink) {                      // a logit per head that joins the denominator only
+      const float sk = sink[h], m_new = fmaxf(m[u], sk);
+      const float corr = expf(m[u] - m_new);
+      inv = corr / (l[u] * corr + expf(sk - m_new));
+    }
     const int64_t base = ((row0 + i0 + my_row[u]) * H + h) * D;
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) {
@@ -212,13 +218,13 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
 template <int D, bool OUT_BF16>
 int launch_mma(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H, int G,
-               float scale, int window, int keep_first, float softcap, void* out, cudaStream_t st) {
+               float scale, int window, int keep_first, float softcap, const float* sink, void* out, cudaStream_t st) {
   const size_t smem = (size_t)(kRows + 2 * kKeys) * (D + kPadH) * sizeof(bf16);
   static SmemAttr attr = {};
   if (smem > 48 * 1024) PRL_CUDA(ensure_smem(attn_mma_kernel<D, OUT_BF16>, (int)smem, attr));
   dim3 grid((max_q + kRows - 1) / kRows, H, n_seg);
   PRL_CUDA(launch_pdl((attn_mma_kernel<D, OUT_BF16>), grid, dim3(128), smem, st, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt,
-                      max_blocks, page_size, ss, sl, sp, sslot, H, G, scale, window, keep_first, softcap, out));
+                      max_blocks, page_size, ss, sl, sp, sslot, H, G, scale, window, keep_first, softcap, sink, out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
@@ -232,10 +238,10 @@ bool attn_mma_fits(int dim, int vdim, const void* q, const void* k_pool, const v
 
 int attn_mma_launch(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                     const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                    int G, int dim, float scale, int window, int keep_first, float softcap, int out_is_bf16, void* out,
-                    cudaStream_t st) {
-#define PRL_MMA(D) (out_is_bf16 ? launch_mma<D, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, out, st) \
-                                : launch_mma<D, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, out, st))
+                    int G, int dim, float scale, int window, int keep_first, float softcap, const float* sink, int out_is_bf16,
+                    void* out, cudaStream_t st) {
+#define PRL_MMA(D) (out_is_bf16 ? launch_mma<D, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, sink, out, st) \
+                                : launch_mma<D, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, sink, out, st))
   if (dim == 32) return PRL_MMA(32);
   if (dim == 64) return PRL_MMA(64);
   return PRL_MMA(128);

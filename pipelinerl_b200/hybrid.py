@@ -1532,10 +1532,7 @@ class HybridEngine(EngineCore):
         _lib.check(lib.prl_latent_query(P, ld, n, H, a.dim, dr, rk, self.rot_freq[i].data_ptr(), row_pos.data_ptr(), il,
                                         R.yb.data_ptr(), R.q.data_ptr(), f32, st))
         self._mm_heads(R.yb, a.dim, self.uk_t[L.weights_of].data_ptr(), rk * a.dim, n, rk, R.o, H, R.q, kd)
-        pool = self.lat_pool[i].data_ptr()
-        _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
-                                         PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
-                                         rk, a.scale, a.window, 0, 0.0, None, 1, R.ya.data_ptr(), st))
+        self._latent_attention(R, i, a, segs, max_q, seg_pos0, None)
         if a.gate:       # v[h] = W_uv,h o_lat[h] in fp32, times sigmoid(g) element by element
             self._mm_heads(R.ya, rk, self.arena.ptr(w + "mix.uv"), dv * rk, n, dv, R.o, H, None, 0, store=False)
             _lib.check(lib.prl_gate_norm(R.o.data_ptr(), 1, H * dv, P + 4 * (hq + kd), ld, None, 1, H * dv, n, H * dv, 1, 0, 0,
@@ -1667,21 +1664,29 @@ class HybridEngine(EngineCore):
                                         row_pos.data_ptr(), 0, R.yb.data_ptr(), R.q.data_ptr(), f32, st))
         # q_lat[h] = W_uk,h^T q_h: per-head products over column blocks of the row buffers, into the attention query
         self._mm_heads(R.yb, a.dim, self.uk_t[L.weights_of].data_ptr(), rk * a.dim, n, rk, R.o, H, R.q, kd)
-        pool = self.lat_pool[i].data_ptr()
         sink = vec[w + "mix.sink"].data_ptr() if a.sink else None
-        if not self.f32 and not self.force_plain_attn and lib.prl_attn_latent_fits(kd, rk, PAGE_SIZE):
-            # bf16: the heads stacked into the M dimension of tensor-core products over the shared key rows
-            _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE,
-                                           seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, kd, rk, a.scale,
-                                           sink, R.ya.data_ptr(), self.attn_ws.data_ptr(), self.attn_ws.numel(), st))
-        else:
-            _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
-                                             PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
-                                             rk, a.scale, 0, 0, 0.0, sink, 1, R.ya.data_ptr(), st))
+        self._latent_attention(R, i, a, segs, max_q, seg_pos0, sink)
         # v[h] = W_uv,h o_lat[h], then the output projection over the concatenated heads
         self._mm_heads(R.ya, rk, self.arena.ptr(w + "mix.uv"), a.vdim * rk, n, a.vdim, R.o, H, R.yb, a.vdim)
         k0 = self._mm(R.yb, H * a.vdim, w + "mix.o", W, R.y0, n, split=True)
         return R.y0, k0, (P + 4 * (a.q_rank + kd)) if L.gated else None, ld
+
+    def _latent_attention(self, R, i, a, segs, max_q, seg_pos0, sink=None) -> None:
+        """Attention of the query R.q [n][H][kv_rank + rot_dim] over run i's latent cache, as ONE shared key head whose
+        values are the rows' first kv_rank channels, into R.ya (operand type).  bf16 with sizes the tensor-core kernel
+        is built for: the heads stacked into the M dimension of its products; else the any-geometry kernel."""
+        lib, f32 = self.lib, int(self.f32)
+        seg_start, seg_len, seg_slot, ns = segs
+        H, rk, kd, pool = a.heads, a.kv_rank, a.kv_rank + a.rot_dim, self.lat_pool[i].data_ptr()
+        if not self.f32 and not self.force_plain_attn and lib.prl_attn_latent_fits(kd, rk, PAGE_SIZE):
+            _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE,
+                                           seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, kd, rk, a.scale,
+                                           a.window, sink, R.ya.data_ptr(), self.attn_ws.data_ptr(), self.attn_ws.numel(),
+                                           self._st))
+        else:
+            _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), pool, pool, kd, f32, self.block_table.data_ptr(), self.max_blocks,
+                                             PAGE_SIZE, seg_start, seg_len, seg_pos0.data_ptr(), seg_slot, ns, max_q, H, 1, kd,
+                                             rk, a.scale, a.window, 0, 0.0, sink, 1, R.ya.data_ptr(), self._st))
 
     def _head_table(self, n: int, heads: int):
         """Tile table of the grouped GEMM (csrc/moe_ops.cu) for per-head products over token-major buffers: the rows

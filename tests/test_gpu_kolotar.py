@@ -384,3 +384,30 @@ def test_trace_runner_command_line(cuda_device, tmp_path):
         for i, ref in expect.items():
             got = torch.from_numpy(np.fromfile(out / f"{i}.f32", dtype="<f4")).view(-1, config["vocab"])
             assert got.shape == ref.shape and kc.rel_err(got, ref) < tol
+
+
+@pytest.mark.parametrize("dim,window", [(32, 100), (64, 64), (128, 37)])
+def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, window):
+    """bf16 with head sizes the tensor-core prompt kernel is built for: the sink joins its denominator after the last key
+    tile.  Strong sinks and peaked scores over five page borders, against the CUDA-core kernel on the same cache (they
+    differ by the bf16 rounding of the softmax weights) and against the oracle; then the latent layer's tensor-core
+    kernel with its window, portions and single tokens."""
+    config = kc.model([A(heads=4, kv_heads=2, dim=dim, vdim=dim, rot_dims=dim // 2, window=window, scale=2.0 * dim ** -0.5),
+                       T(heads=6, dim=16, rot_dim=16, vdim=24, kv_rank=32, window=window, scale=0.6)], width=64)
+    wt = kc.weights(config, 9)
+    wt["l0.mix.sink"] = kc.bf16_round(wt["l0.mix.sink"] * 2.0 + 3.0)
+    toks = kc.tokens_for(config, 330, seed=3)
+    ref = kc.oracle_logits(config, wt, toks)
+    eng = kc.build_engine(config, wt, torch.bfloat16, cuda_device, prefill_chunk=512)
+    assert eng.lib.prl_attn_latent_fits(48, 32, 64)
+    plans = ([330], [63, 17, 16, 130, 65, 20, 3, 2], [300])                 # the rest one by one
+    fast = [kc.stream_logits(eng, toks, p) for p in plans]
+    eng.force_plain_attn = True
+    eng.lib.prl_attn_any_tensor_cores(0)
+    try:
+        plain = [kc.stream_logits(eng, toks, p) for p in plans]
+    finally:
+        eng.lib.prl_attn_any_tensor_cores(1)
+    for f, p in zip(fast, plain):
+        assert 0 < kc.rel_err(f, p) < 0.25 * BF16_TOL                        # two kernels, the same result
+        assert kc.rel_err(f, ref) < BF16_TOL and kc.rel_err(p, ref) < BF16_TOL

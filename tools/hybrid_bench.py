@@ -82,6 +82,28 @@ def pametar_config(s):
                 loop=dict(start=0, stop=2, times=2))
 
 
+def kolotar_config(s):
+    """Eight layers, (windowed attention, windowed attention, latent attention, attention without a softmax beside the
+    gated delta rule) twice: attention heads of 128 with 64 rotated channels and a window of 1024, a latent of 256 with 64
+    rotated channels, delta-rule heads of 128 x 128 on half as many q / k heads, every layer with routed experts of the
+    same active width as the dense ff (four of sixteen experts of ff / 4)."""
+    W, ff, H, G = s["width"], s["ff"], s["heads"], s["kv"]
+    routed = dict(kind="moe", router=dict(experts=16, top=4), expert=dict(ff=ff // 4))
+    att = dict(type="attention", mlp=routed,
+               mixer=dict(heads=H, kv_heads=G, dim=128, vdim=128, mask=dict(size=1024), scale=128 ** -0.5, v_mix=True,
+                          rot=dict(base=1e6, dims=64, scaling=dict(factor=4.0, original=2048, fast=32.0, slow=1.0))))
+    lat = dict(type="latent_attention", mlp=routed,
+               mixer=dict(heads=H, dim=128, rot_dim=64, vdim=128, kv_rank=256, mask=dict(size=1024), rot=dict(dims=64, base=1e4),
+                          scale=192 ** -0.5))
+    par = dict(type="parallel", mlp=routed,
+               mixer=dict(left=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0,
+                                    q_temp=dict(coef=0.1, every=256)),
+                          right=dict(heads=W // 128, kv_heads=max(1, W // 256), dim=128, vdim=128, conv=4),
+                          left_scale=0.5, right_scale=0.5))
+    return dict(architecture="Kolotar", vocab=s["vocab"], width=W, norm=dict(eps=1e-5), postln_alpha=2.0,
+                layers=[[att, att, lat, par][i % 4] for i in range(s["layers"])])
+
+
 def peaks():
     try:
         p = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
@@ -545,6 +567,154 @@ def run_pametar(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=Tr
     return res
 
 
+def run_kolotar(sizes, prompt, context, batch, steps, warm, kernels=True, e2e=True, others=True):
+    """Kolotar beside Pametar (the closest design: latent attention, a delta-rule memory, routed experts in every layer)
+    and the Qwen2 engine at equal width / depth / active ff / attention heads."""
+    from pipelinerl_b200.engine import DecodeEngine
+    from pipelinerl_b200.hybrid import HybridConfig, HybridEngine
+    from pipelinerl_b200.model import ModelConfig, ParamArena
+    dev = torch.device("cuda:0")
+    timer = Timer()
+    res = {}
+    for name in sizes:
+        s = SIZES[name]
+        kw = dict(max_batch=batch, max_seq_len=max(prompt, context) + 256, max_new_tokens=warm + steps + 8, device=dev,
+                  prefill_chunk=1024)
+        entry = {}
+        if e2e and others:
+            qcfg = ModelConfig(vocab_size=s["vocab"], hidden_size=s["width"], intermediate_size=s["ff"], num_layers=s["layers"],
+                               num_q_heads=s["heads"], num_kv_heads=s["kv"])
+            eng = DecodeEngine(qcfg, ParamArena(qcfg, dev).init_random(seed=1), **kw)
+            entry["qwen2"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["qwen2"]["params_M"] = round(qcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+            pcfg = HybridConfig.from_pametar(pametar_config(s))
+            eng = HybridEngine(pcfg, ParamArena(pcfg, dev).init_random(seed=1), **kw)
+            entry["pametar"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["pametar"]["params_M"] = round(pcfg.num_params() / 1e6)
+            del eng
+            torch.cuda.empty_cache()
+        kcfg = HybridConfig.from_kolotar(kolotar_config(s))
+        eng = HybridEngine(kcfg, ParamArena(kcfg, dev).init_random(seed=1), **kw)
+        if e2e:
+            entry["kolotar"] = end_to_end(eng, s["vocab"], prompt, context, batch, steps, warm)
+            entry["kolotar"]["params_M"] = round(kcfg.num_params() / 1e6)
+            for other in ("qwen2", "pametar"):
+                if other in entry:
+                    entry[f"kolotar_over_{other}"] = {k: round(entry["kolotar"][f"{k}_tokens_per_s"] / entry[other][f"{k}_tokens_per_s"], 3)
+                                                      for k in ("prefill", "decode")}
+        if kernels:
+            entry["kernels"] = kernel_table_kolotar(eng, s, batch, 1024, timer)
+        res[name] = entry
+        del eng
+        torch.cuda.empty_cache()
+    return res
+
+
+def kernel_table_kolotar(eng, s, batch, chunk, timer):
+    """The parts of the three Kolotar layer kinds alone, at the decode shape (`batch` one-token segments at position 2047)
+    and the prefill shape (one segment of `chunk` rows whose sequence already holds `chunk` tokens): the engine's own
+    mixer and feed-forward methods on its buffers, then single kernels; memory-bound ones against the measured copy
+    bandwidth, attention products against the measured bf16 GEMM rate, the recurrence against the SMs' fp32 FMA rate."""
+    from pipelinerl_b200 import _lib
+    from pipelinerl_b200.cache import PAGE_SIZE
+    from pipelinerl_b200.hybrid import _Rows
+    lib, cfg = eng.lib, eng.cfg
+    hbm, tflops, how = peaks()
+    fma_tflops = 148 * 128 * 2 * 1.965e9 / 1e12
+    W = cfg.width
+    idx = {k: next(i for i, L in enumerate(cfg.layers) if L.kind == k) for k in ("attention", "latent_attention", "sigmoid_delta")}
+    ai, ti, pi = idx["attention"], idx["latent_attention"], idx["sigmoid_delta"]
+    LA, LT, LP = cfg.layers[ai], cfg.layers[ti], cfg.layers[pi]
+    a, t_, left, g, e = LA.attn, LT.latent, LP.attn, LP.gdelta, LA.mlp.moe
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "fp32_fma_tflops": round(fma_tflops, 1), "source": how}}
+    i32 = dict(dtype=torch.int32, device=eng.dev)
+    ctx = 2047
+    pages_per = (ctx + PAGE_SIZE) // PAGE_SIZE
+    for b in range(batch):
+        eng.block_table[b, :pages_per].copy_(torch.arange(1 + b * pages_per, 1 + (b + 1) * pages_per, **i32))
+    for pools in (eng.lat_pool, eng.k_pool, eng.v_pool):
+        for pool in pools.values():
+            pool.normal_(0, 0.5)
+    for shape, n, ns in (("decode", batch, batch), ("prefill", chunk, 1)):
+        R = _Rows(eng, n)
+        R.P.normal_(0, 0.5); R.xa.normal_(0, 0.5); R.x.normal_(0, 0.5); R.q.normal_(0, 0.5)
+        pos0 = ctx if shape == "decode" else chunk
+        if shape == "decode":
+            R.seg.copy_(torch.stack([torch.arange(n, **i32), torch.ones(n, **i32), torch.full((n,), ctx, **i32), torch.arange(n, **i32)]))
+            R.row_slot.copy_(torch.arange(n, **i32)); R.row_pos.fill_(ctx)
+        else:
+            R.seg[:, :1].copy_(torch.tensor([[0], [n], [pos0], [0]], **i32))
+            R.row_slot.zero_(); R.row_pos.copy_(torch.arange(pos0, pos0 + n, **i32)); R.row_back.copy_(torch.arange(n, **i32))
+        eng._st = _lib.stream_ptr()
+        segs = (R.seg[0].data_ptr(), R.seg[1].data_ptr(), R.seg[3].data_ptr(), ns)
+        max_q = 1 if shape == "decode" else n
+        wa, wt_, wp = f"l{LA.weights_of}.", f"l{LT.weights_of}.", f"l{LP.weights_of}."
+        t = {}
+        t["attention_mixer"] = timer.events(lambda: eng._window_attn_mixer(R, n, ai, LA, wa, segs, max_q, R.row_pos, R.seg[2]))
+        t["latent_mixer"] = timer.events(lambda: eng._latent_direct_mixer(R, n, ti, LT, wt_, segs, max_q, R.row_pos, R.seg[2]))
+        t["sigmoid_delta_mixer"] = timer.events(lambda: eng._sigmoid_delta_mixer(R, n, pi, LP, wp, segs, max_q, R.row_pos, R.seg[2]))
+        t["routed_ff"] = timer.events(lambda: eng._routed_ff(R, n, wa, e, 1.0))
+        t["postln_close"] = timer.events(lambda: eng._postln_close(R, n, wa, "1", R.y0, 1))
+        bt, mb = eng.block_table.data_ptr(), eng.max_blocks
+
+        def win_attn():
+            _lib.check(lib.prl_attn_any_sink(R.q.data_ptr(), eng.k_pool[ai].data_ptr(), eng.v_pool[ai].data_ptr(), a.vdim, 0, bt, mb,
+                                             PAGE_SIZE, *segs[:2], R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, a.kv_heads, a.dim,
+                                             a.vdim, a.scale, a.window, 0, 0.0, eng.vec[wa + "mix.sink"].data_ptr(), 0, R.o.data_ptr(),
+                                             eng._st))
+        kd = t_.kv_rank + t_.rot_dim
+        pool = eng.lat_pool[ti].data_ptr()
+
+        def lat_attn():
+            eng._latent_attention(R, ti, t_, segs, max_q, R.seg[2])
+
+        def sig_attn():
+            _lib.check(lib.prl_attn_sigmoid(R.q.data_ptr(), eng.k_pool[pi].data_ptr(), eng.v_pool[pi].data_ptr(), 0, bt, mb, PAGE_SIZE,
+                                            *segs[:2], R.seg[2].data_ptr(), segs[2], ns, max_q, left.heads, left.kv_heads, left.dim,
+                                            left.vdim, left.scale, left.softcap, left.q_temp[0], left.q_temp[1],
+                                            eng.vec[wp + "mix.left.pb"].data_ptr(), eng.vec[wp + "mix.left.talk"].data_ptr(), 1,
+                                            R.ya.data_ptr(), eng._st))
+        gq, gv, ch = g.kv_heads * g.dim, g.heads * g.vdim, g.conv_channels
+        nleft = left.heads * left.dim + left.kv_heads * (left.dim + left.vdim)
+        ldp = nleft + g.in_rows
+
+        def scan():
+            _lib.check(lib.prl_gated_delta_scan(R.aux.data_ptr(), ch, 0, gq, 2 * gq, R.P.data_ptr(), ldp, nleft + ch, nleft + ch + g.heads,
+                                                eng.vec[wp + "mix.right.A_log"].data_ptr(), eng.vec[wp + "mix.right.dt_bias"].data_ptr(),
+                                                g.unit_eps, g.heads, g.kv_heads, g.dim, g.vdim, n, R.dprep.data_ptr(), *segs[:3], ns, max_q,
+                                                eng.delta_state[pi].data_ptr(), R.o.data_ptr(), gv, eng._st))
+        t["window_attention"] = timer.events(win_attn)
+        t["latent_attention"] = timer.events(lat_attn)
+        t["sigmoid_attention"] = timer.events(sig_attn, iters=3, warm=1)
+        t["gated_delta_scan"] = timer.events(scan)
+        row = {k: {"us": round(v * 1e3, 1)} for k, v in t.items()}
+        # (query, key) pairs a row really sees
+        seen_w = [min(a.window, p + 1) for p in (range(pos0, pos0 + n) if shape == "prefill" else [ctx] * n)]
+        seen_t = [min(t_.window, p + 1) for p in (range(pos0, pos0 + n) if shape == "prefill" else [ctx] * n)]
+        seen_all = [p + 1 for p in (range(pos0, pos0 + n) if shape == "prefill" else [ctx] * n)]
+        fl = {"window_attention": 2.0 * sum(seen_w) * a.heads * (a.dim + a.vdim),
+              "latent_attention": 2.0 * sum(seen_t) * t_.heads * (kd + t_.kv_rank),
+              "sigmoid_attention": 2.0 * sum(seen_all) * left.heads * (left.dim + left.vdim + left.heads)}
+        for k, f in fl.items():
+            row[k]["tflops"] = round(f / t[k] / 1e9, 1)
+            row[k]["of_bf16_peak"] = round(f / t[k] / 1e9 / tflops, 4)
+        if shape == "decode":
+            row["window_attention"]["of_hbm"] = round(sum(seen_w) * a.kv_heads * (a.dim + a.vdim) * 2 / t["window_attention"] / 1e6 / hbm, 3)
+            row["latent_attention"]["of_hbm"] = round(sum(seen_t) * kd * 2 / t["latent_attention"] / 1e6 / hbm, 3)
+            row["sigmoid_attention"]["of_hbm"] = round(sum(seen_all) * left.kv_heads * (left.dim + left.vdim) * 2 / t["sigmoid_attention"] / 1e6 / hbm, 3)
+            row["gated_delta_scan"]["of_hbm"] = round(2 * n * g.heads * g.dim * g.vdim * 4 / t["gated_delta_scan"] / 1e6 / hbm, 3)
+        else:
+            row["gated_delta_scan"]["of_fp32_fma"] = round(n * g.heads * g.dim * g.vdim * 5 * 2 / t["gated_delta_scan"] / 1e9 / fma_tflops, 3)
+        row["postln_close"]["of_hbm"] = round((n * W * 4 * 3 + n * W * 2) / t["postln_close"] / 1e6 / hbm, 3)
+        out[shape] = row
+        del R
+    eng.block_table.zero_()
+    eng.states.reset(0)
+    return out
+
+
 def kernel_table_pametar(eng, s, batch, chunk, timer):
     """The parts of a Pametar layer alone, at the decode shape (`batch` one-token segments at position 2047) and the
     prefill shape (one segment of `chunk` rows whose sequence already holds `chunk` tokens): the engine's own mixer and
@@ -596,7 +766,7 @@ def kernel_table_pametar(eng, s, batch, chunk, timer):
 
         def attn():
             _lib.check(lib.prl_attn_latent(R.q.data_ptr(), pool, eng.block_table.data_ptr(), eng.max_blocks, PAGE_SIZE, *segs[:2],
-                                           R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, kd, a.kv_rank, a.scale,
+                                           R.seg[2].data_ptr(), segs[2], ns, max_q, a.heads, kd, a.kv_rank, a.scale, 0,
                                            eng.vec[wa + "mix.sink"].data_ptr(), R.ya.data_ptr(), eng.attn_ws.data_ptr(),
                                            eng.attn_ws.numel(), eng._st))
 
@@ -680,12 +850,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-kernels", action="store_true")
     ap.add_argument("--only-kernels", action="store_true", help="skip the end-to-end runs (a small case for a profiler)")
-    ap.add_argument("--design", default="povurax", choices=["povurax", "belelorn", "pametar"], help="which hybrid design is measured")
+    ap.add_argument("--design", default="povurax", choices=["povurax", "belelorn", "pametar", "kolotar"], help="which hybrid design is measured")
     ap.add_argument("--alone", action="store_true", help="--design belelorn: skip the Qwen2 and Povurax runs beside it")
     a = ap.parse_args()
     from pipelinerl_b200 import _lib
     before = _lib.launch_count()
-    if a.design == "pametar":
+    if a.design == "kolotar":
+        res = run_kolotar(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels,
+                          e2e=not a.only_kernels, others=not a.alone)
+    elif a.design == "pametar":
         res = run_pametar(a.sizes.split(","), a.prompt, a.context, a.batch, a.steps, a.warmup, kernels=not a.no_kernels,
                           e2e=not a.only_kernels, others=not a.alone)
     elif a.design == "belelorn":
