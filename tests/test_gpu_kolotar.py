@@ -411,3 +411,35 @@ def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, win
     for f, p in zip(fast, plain):
         assert 0 < kc.rel_err(f, p) < 0.25 * BF16_TOL                        # two kernels, the same result
         assert kc.rel_err(f, ref) < BF16_TOL and kc.rel_err(p, ref) < BF16_TOL
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 32, 32), (6, 3, 16, 64), (20, 4, 16, 128), (3, 1, 48, 128)])
+def test_tensor_core_attention_without_a_softmax(cuda_device, heads, kv_heads, dim, vdim):
+    """bf16 with sizes the tensor-core kernel is built for (more output heads than one CTA holds in one case): prompt
+    portions, mixed batches and single tokens (whose keys are split over CTAs and added afterwards) against the
+    CUDA-core kernel on the same cache (they differ by the bf16 rounding of the mixed weights) and against the oracle.
+    Weights kept small by the head bias so that 330 unnormalised terms stay O(1)."""
+    config = kc.model([P(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, q_temp=(0.7, 48), softcap=8.0, left_scale=1.0,
+                         right_scale=0.1)], width=64)
+    wt = kc.weights(config, 9)
+    wt["l0.mix.left.pb"] = kc.bf16_round(wt["l0.mix.left.pb"] - 3.0)
+    toks = kc.tokens_for(config, 330, seed=3)
+    ref = kc.oracle_logits(config, wt, toks)
+    eng = kc.build_engine(config, wt, torch.bfloat16, cuda_device, prefill_chunk=512)
+    assert eng.lib.prl_attn_sigmoid_tc_fits(heads, kv_heads, dim, vdim)
+    plans = ([330], [63, 17, 16, 130, 65, 20, 3, 2], [300])                 # the rest one by one
+    fast = [kc.stream_logits(eng, toks, p) for p in plans]
+    eng.force_plain_attn = True
+    plain = [kc.stream_logits(eng, toks, p) for p in plans]
+    for f, p in zip(fast, plain):
+        assert 0 < kc.rel_err(f, p) < 0.25 * BF16_TOL
+        assert kc.rel_err(f, ref) < BF16_TOL and kc.rel_err(p, ref) < BF16_TOL
+    # a mixed batch: a portion beside single tokens of other sequences
+    eng.force_plain_attn = False
+    a, b, c = eng.open_stream(), eng.open_stream(), eng.open_stream()
+    eng.feed([(b, toks[:70], []), (c, toks[:129], [])])
+    got = eng.feed([(a, toks[:100], list(range(100))), (b, toks[70:71], [0]), (c, toks[129:130], [0])]).double().cpu()
+    assert kc.rel_err(got[:100], ref[:100]) < BF16_TOL and kc.rel_err(got[100:101], ref[70:71]) < BF16_TOL
+    assert kc.rel_err(got[101:], ref[129:130]) < BF16_TOL
+    for s in (a, b, c):
+        eng.close_stream(s)
