@@ -832,12 +832,12 @@ int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v_pool, int3
                      int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
                      const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H, int32_t G,
                      int32_t dim, int32_t vdim, float scale, float softcap, float temp_coef, float temp_every,
-                     const float* head_bias, const float* talk, int32_t out_is_t, void* out,
+                     const float* head_bias, const float* talk, int32_t out_is_t, void* out, int32_t n_rows /* of q and out */,
                      int32_t allow_tc /* bf16, out_is_t, prl_attn_sigmoid_tc_fits: the tensor-core kernel */,
                      void* ws /* prl_attn_sigmoid_workspace_bytes, or NULL: a decode step's keys are not split */,
                      size_t ws_bytes, prl_stream_t stream);
 int32_t prl_attn_sigmoid_tc_fits(int32_t H, int32_t G, int32_t dim, int32_t vdim);
-size_t prl_attn_sigmoid_workspace_bytes(int32_t n_seg, int32_t H, int32_t vdim);
+size_t prl_attn_sigmoid_workspace_bytes(int32_t n_rows, int32_t n_seg, int32_t max_q, int32_t H, int32_t vdim);
 /* S <- g S; d = beta (v - S^T k); S <- S + k d^T; o = S^T q with unit q (times dk^(-1/2)) and k, beta = sigmoid(Z[off_b + h]),
  * g = exp(-exp(A_log[h]) softplus(Z[off_a + h] + dt_bias[h])); `kh` q / k heads serve `heads` value heads; scratch
  * [n_rows][5 * heads * dk] fp32; state [slot][head][dv][dk] fp32 */

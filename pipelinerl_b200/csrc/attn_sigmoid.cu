@@ -272,23 +272,38 @@ __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(Sigmo
       for (int e = 0; e < 4; ++e) o[i][j][e] = 0.f;
 
   const int chk = dim / 8, chv = vdim / 8;
-  for (int t = t_begin; t < t_end; ++t) {
+  // The K and V tiles are copied as groups of their own: V of a tile arrives while its scores are formed, K of the next
+  // tile while this tile's weights meet the values.
+  auto stage_k = [&](int t) {
+    if (t < t_end) {
+      const int k0 = t * kKeys;
+      const int64_t page = bt[k0 / a.page_size];
+      const int in_page = k0 % a.page_size;
+      for (int c = tid; c < G * kKeys * chk; c += blockDim.x) {
+        const int row = c / chk, cc = c - row * chk, g = row / kKeys, j = row - g * kKeys;
+        const bool ok = k0 + j <= last_pos;
+        cp16z(Ks + (size_t)row * ldk + cc * 8, k_pool + ((page * G + g) * a.page_size + in_page + (ok ? j : 0)) * dim + cc * 8, ok ? 16 : 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto stage_v = [&](int t) {
     const int k0 = t * kKeys;
-    __syncthreads();                                            // the previous tile's readers are done
     const int64_t page = bt[k0 / a.page_size];
     const int in_page = k0 % a.page_size;
-    for (int c = tid; c < G * kKeys * chk; c += blockDim.x) {
-      const int row = c / chk, cc = c - row * chk, g = row / kKeys, j = row - g * kKeys;
-      const bool ok = k0 + j <= last_pos;
-      cp16z(Ks + (size_t)row * ldk + cc * 8, k_pool + ((page * G + g) * a.page_size + in_page + (ok ? j : 0)) * dim + cc * 8, ok ? 16 : 0);
-    }
     for (int c = tid; c < G * kKeys * chv; c += blockDim.x) {
       const int row = c / chv, cc = c - row * chv, g = row / kKeys, j = row - g * kKeys;
       const bool ok = k0 + j <= last_pos;
       cp16z(Vs + (size_t)row * ldv + cc * 8, v_pool + ((page * G + g) * a.page_size + in_page + (ok ? j : 0)) * vdim + cc * 8, ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+  stage_k(t_begin);
+  for (int t = t_begin; t < t_end; ++t) {
+    const int k0 = t * kKeys;
+    __syncthreads();                                            // the previous tile's values are read
+    stage_v(t);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");        // the queries and this tile's keys are here
     __syncthreads();
     // (1) the sigmoid weights of the source heads, 16 rows x 32 keys each
     for (int g = warp; g < H; g += kTcWarps) {
@@ -309,23 +324,30 @@ __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(Sigmo
         mma16816(s[2], af, b23[0], b23[1]);
         mma16816(s[3], af, b23[2], b23[3]);
       }
-      const float bias = pb[g];
+      const float bias = pb[g], cap_inv = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
       float* wg = Wt + (size_t)g * kTcRows * kWtLd;
 #pragma unroll
       for (int j = 0; j < 4; ++j)
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-          float w[2];
+          float w[2] = {0.f, 0.f};
 #pragma unroll
           for (int b = 0; b < 2; ++b) {
             const int key = k0 + 8 * j + t2 + b;
-            float v = s[j][2 * u + b] * srow[gid + 8 * u];
-            if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
-            w[b] = key <= pos_r[u] ? 1.f / (1.f + expf(-(v + bias))) : 0.f;
+            if (key <= pos_r[u]) {                              // (no such row: pos_r = -1)
+              float v = s[j][2 * u + b] * srow[gid + 8 * u];
+              // tanh(x) = 1 - 2 / (e^(2x) + 1) and the sigmoid through the exponential unit: absolute errors of a few
+              // 1e-7, far below the bf16 rounding of the weights that follows
+              if (a.softcap > 0.f) v = a.softcap * (1.f - __fdividef(2.f, __expf(2.f * v * cap_inv) + 1.f));
+              w[b] = __fdividef(1.f, 1.f + __expf(-(v + bias)));
+            }
           }
           *reinterpret_cast<float2*>(wg + (gid + 8 * u) * kWtLd + 8 * j + t2) = make_float2(w[0], w[1]);
         }
     }
+    __syncthreads();                                            // the weights are written, the keys are read
+    stage_k(t + 1);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");        // this tile's values are here
     __syncthreads();
     // (2) + (3) this warp's output heads: mix, round, multiply with the values
 #pragma unroll
@@ -421,27 +443,29 @@ extern "C" int32_t prl_attn_sigmoid_tc_fits(int32_t H, int32_t G, int32_t dim, i
          sigmoid_tc_smem(H, G, dim, vdim) <= 200 * 1024;
 }
 
-// CTAs that share the key tiles of a batch of short segments, and the fp32 workspace their shares need
-static int sigmoid_splits(int n_seg, int H, int vdim) {
+// CTAs that share the key tiles of a row tile when the batch has fewer row tiles than the GPU has SMs (a decode step, a
+// short prompt portion), and the fp32 workspace their shares need: [splits][n_rows][H][vdim]
+static int sigmoid_splits(int n_seg, int max_q, int H, int vdim) {
   const int per_cta = kTcWarps * (256 / vdim);                  // output heads one CTA holds
-  const int units = n_seg * ((H + per_cta - 1) / per_cta);
-  int s = num_sms() / (units > 0 ? units : 1);
-  return s < 1 ? 1 : (s > 8 ? 8 : s);
+  const int64_t units = (int64_t)n_seg * ((max_q + kTcRows - 1) / kTcRows) * ((H + per_cta - 1) / per_cta);
+  const int64_t s = num_sms() / (units > 0 ? units : 1);
+  return s < 1 ? 1 : (s > 8 ? 8 : (int)s);
 }
-extern "C" size_t prl_attn_sigmoid_workspace_bytes(int32_t n_seg, int32_t H, int32_t vdim) {
-  return (size_t)sigmoid_splits(n_seg, H, vdim) * n_seg * H * vdim * sizeof(float);
+extern "C" size_t prl_attn_sigmoid_workspace_bytes(int32_t n_rows, int32_t n_seg, int32_t max_q, int32_t H, int32_t vdim) {
+  const int splits = sigmoid_splits(n_seg, max_q, H, vdim);
+  return splits > 1 ? (size_t)splits * n_rows * H * vdim * sizeof(float) : 0;
 }
 
 // q [n][H][dim] and the pools in fp32 (f32) or bf16; head_bias [H] and talk [H][H] fp32 (NULL: no bias / no mixing);
 // out [n][H][vdim] in the cache's element type (out_is_t) or fp32.  temp_coef == 0: no query temperature.
-// allow_tc: bf16 with out_is_t and a geometry of prl_attn_sigmoid_tc_fits takes the tensor-core kernel; a batch whose
-// segments are single tokens then splits a segment's keys over CTAs if ws holds prl_attn_sigmoid_workspace_bytes.
+// allow_tc: bf16 with out_is_t and a geometry of prl_attn_sigmoid_tc_fits takes the tensor-core kernel; a batch with few
+// row tiles then splits their keys over CTAs if ws holds prl_attn_sigmoid_workspace_bytes (n_rows = rows of q and out).
 extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v_pool, int32_t f32, const int32_t* block_table,
                                 int32_t max_blocks, int32_t page_size, const int32_t* seg_start, const int32_t* seg_len,
                                 const int32_t* seg_pos0, const int32_t* seg_slot, int32_t n_seg, int32_t max_q, int32_t H,
                                 int32_t G, int32_t dim, int32_t vdim, float scale, float softcap, float temp_coef,
                                 float temp_every, const float* head_bias, const float* talk, int32_t out_is_t, void* out,
-                                int32_t allow_tc, void* ws, size_t ws_bytes, prl_stream_t st) {
+                                int32_t n_rows, int32_t allow_tc, void* ws, size_t ws_bytes, prl_stream_t st) {
   PRL_CHECK_ARG(q && k_pool && v_pool && block_table && seg_start && seg_len && seg_pos0 && seg_slot && out,
                 "prl_attn_sigmoid: NULL argument");
   PRL_CHECK_ARG(n_seg >= 1 && n_seg <= 65535 && max_q >= 1 && H >= 1 && G >= 1 && H % G == 0 && dim >= 1 && vdim >= 1 &&
@@ -453,11 +477,11 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
       ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) && ((uintptr_t)out & 3) == 0) {
     const int per_cta = kTcWarps * (256 / vdim);
     const int groups = (H + per_cta - 1) / per_cta;
-    int splits = 1;
-    if (max_q == 1 && ws && ws_bytes >= prl_attn_sigmoid_workspace_bytes(n_seg, H, vdim)) splits = sigmoid_splits(n_seg, H, vdim);
+    int splits = sigmoid_splits(n_seg, max_q, H, vdim);
+    if (!ws || n_rows < 1 || ws_bytes < prl_attn_sigmoid_workspace_bytes(n_rows, n_seg, max_q, H, vdim)) splits = 1;
     SigmoidTcArgs ta{{q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot,
                       H, G, dim, vdim, scale, softcap, temp_coef, temp_every, head_bias, talk, 0, out},
-                     splits, (int64_t)n_seg, (float*)ws};
+                     splits, (int64_t)n_rows, (float*)ws};
     const size_t smem = sigmoid_tc_smem(H, G, dim, vdim);
     dim3 grid((max_q + kTcRows - 1) / kTcRows, n_seg, splits * groups);
     static SmemAttr attr[3] = {};
@@ -472,7 +496,7 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
 #undef PRL_SIGTC
     PRL_LAUNCH_CHECK();
     if (splits > 1) {
-      const int64_t n = (int64_t)n_seg * H * vdim;
+      const int64_t n = (int64_t)n_rows * H * vdim;
       PRL_CUDA(launch_pdl(attn_sigmoid_merge_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, s, (const float*)ws, n,
                           splits, (bf16*)out));
       PRL_LAUNCH_CHECK();

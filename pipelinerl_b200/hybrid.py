@@ -1126,9 +1126,13 @@ class HybridEngine(EngineCore):
             if L.latent is not None:
                 for n_seg in range(1, max(B, 4) + 1):     # the split count falls as the batch grows; the product need not
                     ws = max(ws, int(lib.prl_attn_latent_workspace_bytes(n_seg, L.latent.heads, L.latent.kv_rank)))
-            elif L.kind == "sigmoid_delta":               # attention without a softmax: the key splits' shares likewise
+            elif L.kind == "sigmoid_delta" and not self.f32:
+                # attention without a softmax: the shares of CTAs that split a row tile's keys.  A decode step of up to B
+                # single tokens; a packed batch never needs more than 8 shares of <= 16 rows per SM-filling unit
+                a = L.attn
                 for n_seg in range(1, max(B, 4) + 1):
-                    ws = max(ws, int(lib.prl_attn_sigmoid_workspace_bytes(n_seg, L.attn.heads, L.attn.vdim)))
+                    ws = max(ws, int(lib.prl_attn_sigmoid_workspace_bytes(n_seg, n_seg, 1, a.heads, a.vdim)))
+                ws = max(ws, 16 * 160 * a.heads * a.vdim * 4)
         self.attn_ws = torch.zeros(max(ws, 16), dtype=torch.uint8, device=d)
         self._dec = _Rows(self, B)
         i32 = dict(dtype=torch.int32, device=d)
@@ -1564,7 +1568,7 @@ class HybridEngine(EngineCore):
                                         self.block_table.data_ptr(), self.max_blocks, PAGE_SIZE, seg_start, seg_len,
                                         seg_pos0.data_ptr(), seg_slot, ns, max_q, a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
                                         a.softcap, a.q_temp[0], a.q_temp[1], vec[w + "mix.left.pb"].data_ptr(),
-                                        vec[w + "mix.left.talk"].data_ptr() if a.talking else None, 1, R.ya.data_ptr(),
+                                        vec[w + "mix.left.talk"].data_ptr() if a.talking else None, 1, R.ya.data_ptr(), n,
                                         int(not self.force_plain_attn), self.attn_ws.data_ptr(), self.attn_ws.numel(), st))
         k0 = self._mm(R.ya, no, w + "mix.left.o", W, R.y0, n, split=True)
         # -- right: convolutions + SiLU over [q | k | v], then the scan

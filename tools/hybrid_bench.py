@@ -675,7 +675,7 @@ def kernel_table_kolotar(eng, s, batch, chunk, timer):
                                             *segs[:2], R.seg[2].data_ptr(), segs[2], ns, max_q, left.heads, left.kv_heads, left.dim,
                                             left.vdim, left.scale, left.softcap, left.q_temp[0], left.q_temp[1],
                                             eng.vec[wp + "mix.left.pb"].data_ptr(), eng.vec[wp + "mix.left.talk"].data_ptr(), 1,
-                                            R.ya.data_ptr(), 1, eng.attn_ws.data_ptr(), eng.attn_ws.numel(), eng._st))
+                                            R.ya.data_ptr(), n, 1, eng.attn_ws.data_ptr(), eng.attn_ws.numel(), eng._st))
         gq, gv, ch = g.kv_heads * g.dim, g.heads * g.vdim, g.conv_channels
         nleft = left.heads * left.dim + left.kv_heads * (left.dim + left.vdim)
         ldp = nleft + g.in_rows
