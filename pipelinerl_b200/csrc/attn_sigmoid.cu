@@ -16,7 +16,7 @@
 // of 32 and every sum runs in ascending key order, so a token's result does not depend on how its prompt was cut or
 // batched.  Everything is fp32; T is only the storage type of q, the cache and (optionally) the output.
 //
-// Tensor-core variant (bf16 cache, dim a multiple of 16, vdim 32 / 64 / 128): CTA = eight warps on ONE tile of 16
+// Tensor-core variant (bf16 cache, dim and vdim multiples of 16, vdim <= 128): CTA = eight warps on ONE tile of 16
 // query rows with all heads.  Per key tile of 32: (1) the warps take the source heads in turn, S = Q K^T by mma.sync
 // m16n8k16 with operands read by ldmatrix from padded rows, temperature, cap, bias, sigmoid and mask in fp32, the
 // weights to shared memory ([H][16][32] fp32); (2) every warp mixes the weights of its own output heads (a dot product
@@ -210,7 +210,10 @@ __host__ __device__ inline size_t sigmoid_tc_smem(int H, int G, int dim, int vdi
          ((size_t)H * kTcRows * kWtLd + (size_t)H * H + H + kTcRows) * sizeof(float);
 }
 
-// NV = vdim / 8 accumulator tiles per head, HPW output heads per warp (NV * HPW = 32: 128 accumulator registers)
+// Output heads per warp for a value size: as many as 128 accumulator registers per thread hold, at most 8
+__host__ __device__ constexpr int sigmoid_tc_hpw(int vdim) { return 256 / vdim > 8 ? 8 : 256 / vdim; }
+
+// NV = vdim / 8 accumulator tiles per head, HPW output heads per warp (NV * HPW <= 32: 128 accumulator registers)
 template <int NV, int HPW>
 __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(SigmoidTcArgs ta) {
   pdl_wait();
@@ -439,14 +442,14 @@ using namespace prl;
 
 // 1 if the tensor-core kernel runs this geometry in bf16 (else prl_attn_sigmoid takes the CUDA-core kernel)
 extern "C" int32_t prl_attn_sigmoid_tc_fits(int32_t H, int32_t G, int32_t dim, int32_t vdim) {
-  return H >= 1 && G >= 1 && H % G == 0 && dim >= 16 && dim % 16 == 0 && (vdim == 32 || vdim == 64 || vdim == 128) &&
+  return H >= 1 && G >= 1 && H % G == 0 && dim >= 16 && dim % 16 == 0 && vdim >= 16 && vdim % 16 == 0 && vdim <= 128 &&
          sigmoid_tc_smem(H, G, dim, vdim) <= 200 * 1024;
 }
 
 // CTAs that share the key tiles of a row tile when the batch has fewer row tiles than the GPU has SMs (a decode step, a
 // short prompt portion), and the fp32 workspace their shares need: [splits][n_rows][H][vdim]
 static int sigmoid_splits(int n_seg, int max_q, int H, int vdim) {
-  const int per_cta = kTcWarps * (256 / vdim);                  // output heads one CTA holds
+  const int per_cta = kTcWarps * sigmoid_tc_hpw(vdim);          // output heads one CTA holds
   const int64_t units = (int64_t)n_seg * ((max_q + kTcRows - 1) / kTcRows) * ((H + per_cta - 1) / per_cta);
   const int64_t s = num_sms() / (units > 0 ? units : 1);
   return s < 1 ? 1 : (s > 8 ? 8 : (int)s);
@@ -475,7 +478,7 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
   cudaStream_t s = (cudaStream_t)st;
   if (!f32 && out_is_t && allow_tc && prl_attn_sigmoid_tc_fits(H, G, dim, vdim) &&
       ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) && ((uintptr_t)out & 3) == 0) {
-    const int per_cta = kTcWarps * (256 / vdim);
+    const int per_cta = kTcWarps * sigmoid_tc_hpw(vdim);
     const int groups = (H + per_cta - 1) / per_cta;
     int splits = sigmoid_splits(n_seg, max_q, H, vdim);
     if (!ws || n_rows < 1 || ws_bytes < prl_attn_sigmoid_workspace_bytes(n_rows, n_seg, max_q, H, vdim)) splits = 1;
@@ -484,15 +487,15 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
                      splits, (int64_t)n_rows, (float*)ws};
     const size_t smem = sigmoid_tc_smem(H, G, dim, vdim);
     dim3 grid((max_q + kTcRows - 1) / kTcRows, n_seg, splits * groups);
-    static SmemAttr attr[3] = {};
-#define PRL_SIGTC(NV, HPW, I)                                                                        \
-  do {                                                                                               \
-    PRL_CUDA(ensure_smem((attn_sigmoid_tc_kernel<NV, HPW>), (int)smem, attr[I]));                    \
-    PRL_CUDA(launch_pdl((attn_sigmoid_tc_kernel<NV, HPW>), grid, dim3(32 * kTcWarps), smem, s, ta)); \
-  } while (0)
-    if (vdim == 32) PRL_SIGTC(4, 8, 0);
-    else if (vdim == 64) PRL_SIGTC(8, 4, 1);
-    else PRL_SIGTC(16, 2, 2);
+    static SmemAttr attr[8] = {};
+#define PRL_SIGTC(NV)                                                                                               \
+  case NV * 8:                                                                                                      \
+    PRL_CUDA(ensure_smem((attn_sigmoid_tc_kernel<NV, sigmoid_tc_hpw(NV * 8)>), (int)smem, attr[NV / 2 - 1]));       \
+    PRL_CUDA(launch_pdl((attn_sigmoid_tc_kernel<NV, sigmoid_tc_hpw(NV * 8)>), grid, dim3(32 * kTcWarps), smem, s, ta)); \
+    break
+    switch (vdim) {
+      PRL_SIGTC(2); PRL_SIGTC(4); PRL_SIGTC(6); PRL_SIGTC(8); PRL_SIGTC(10); PRL_SIGTC(12); PRL_SIGTC(14); PRL_SIGTC(16);
+    }
 #undef PRL_SIGTC
     PRL_LAUNCH_CHECK();
     if (splits > 1) {

@@ -413,7 +413,8 @@ def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, win
         assert kc.rel_err(f, ref) < BF16_TOL and kc.rel_err(p, ref) < BF16_TOL
 
 
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 32, 32), (6, 3, 16, 64), (20, 4, 16, 128), (3, 1, 48, 128)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 32, 32), (6, 3, 16, 64), (20, 4, 16, 128), (3, 1, 48, 128), (6, 2, 80, 48),
+                                                      (2, 2, 16, 16), (5, 5, 32, 112)])
 def test_tensor_core_attention_without_a_softmax(cuda_device, heads, kv_heads, dim, vdim):
     """bf16 with sizes the tensor-core kernel is built for (more output heads than one CTA holds in one case): prompt
     portions, mixed batches and single tokens (whose keys are split over CTAs and added afterwards) against the
