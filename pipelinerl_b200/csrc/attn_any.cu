@@ -25,8 +25,8 @@ namespace prl {
 bool attn_mma_fits(int dim, int vdim, const void* q, const void* k_pool, const void* v_pool);
 int attn_mma_launch(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                     const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                    int G, int dim, float scale, int window, int keep_first, float softcap, const float* sink, int out_is_bf16,
-                    void* out, cudaStream_t st);
+                    int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, const float* sink,
+                    int out_is_bf16, void* out, cudaStream_t st);
 
 namespace {
 
@@ -469,7 +469,7 @@ static int attn_any_impl(const void* q, const void* k_pool, const void* v_pool, 
   const int vr = (vdim + 31) / 32;
   if (!f32 && g_attn_tensor_cores && max_q >= kMmaMinRows && ldv == vdim && attn_mma_fits(dim, vdim, q, k_pool, v_pool))
     return attn_mma_launch(q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot, n_seg,
-                           max_q, H, G, dim, scale, window, keep_first, softcap, sink, out_is_t, out, (cudaStream_t)st);
+                           max_q, H, G, dim, vdim, scale, window, keep_first, softcap, sink, out_is_t, out, (cudaStream_t)st);
   if (f32) return dispatch_attn<float>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,
                                        seg_slot, n_seg, max_q, H, G, dim, vdim, scale, window, keep_first, softcap, ldv, sink, out_is_t, out, (cudaStream_t)st);
   return dispatch_attn<__nv_bfloat16>(vr, q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0,

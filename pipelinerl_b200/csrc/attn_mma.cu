@@ -1,5 +1,5 @@
-// Tensor-core variant of the any-geometry paged attention (attn_any.cu) for prompt portions in bf16: head sizes
-// dim == vdim in {32, 64, 128}, with the same options (sliding window that keeps the first tokens, tanh-capped
+// Tensor-core variant of the any-geometry paged attention (attn_any.cu) for prompt portions in bf16: key sizes that are
+// multiples of 16 (up to 256) and value sizes 16 / 32 / 48 / 64 / 96 / 128, with the same options (sliding window that keeps the first tokens, tanh-capped
 // scores, grouped key/value heads, output in bf16 or fp32).
 //
 // CTA = 4 warps = 64 consecutive query rows of one (segment, query head); a warp owns 16 rows.  Keys are walked in
@@ -46,21 +46,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int D, bool OUT_BF16>
+// D: query / key size, a compile-time number for the square geometries (fully unrolled score loop) or 0 = the run-time
+// `dim_rt`; DV: value size.
+template <int D, int DV, bool OUT_BF16>
 __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool,
                                                        const bf16* __restrict__ v_pool, const int32_t* __restrict__ block_table,
                                                        int max_blocks, int page_size, const int32_t* __restrict__ seg_start,
                                                        const int32_t* __restrict__ seg_len, const int32_t* __restrict__ seg_pos0,
-                                                       const int32_t* __restrict__ seg_slot, int H, int G, float scale,
+                                                       const int32_t* __restrict__ seg_slot, int H, int G, int dim_rt, float scale,
                                                        int window, int keep_first, float softcap, const float* __restrict__ sink,
                                                        void* __restrict__ out_v) {
   pdl_wait();
-  constexpr int LD = D + kPadH;            // halves per staged row: (D + 8) * 2 bytes, a multiple of 16, odd in 16-byte units
-  constexpr int CH = D / 8;                // 16-byte chunks per row
+  const int dim = D ? D : dim_rt;
+  const int LD = dim + kPadH;              // halves per staged row: (dim + 8) * 2 bytes, a multiple of 16, odd in 16-byte units
+  const int CH = dim / 8;                  // 16-byte chunks per row
+  constexpr int LDV = DV + kPadH, CHV = DV / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [64][LD]
   bf16* Ks = Qs + kRows * LD;                        // [64][LD]
-  bf16* Vs = Ks + kKeys * LD;                        // [64][LD]
+  bf16* Vs = Ks + kKeys * LD;                        // [64][LDV]
   const int seg = blockIdx.z, h = blockIdx.y;
   const int len = seg_len[seg];
   const int i0 = blockIdx.x * kRows;
@@ -77,7 +81,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
   for (int c = tid; c < kRows * CH; c += 128) {
     const int r = c / CH, cc = c - r * CH;
     const bool ok = r < rows_here;
-    cp16(Qs + r * LD + cc * 8, q + ((row0 + i0 + (ok ? r : 0)) * H + h) * D + cc * 8, ok ? 16 : 0);
+    cp16(Qs + r * LD + cc * 8, q + ((row0 + i0 + (ok ? r : 0)) * H + h) * dim + cc * 8, ok ? 16 : 0);
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
   // this thread's two rows of the warp's 16: r_lo = lane / 4, r_hi = r_lo + 8
@@ -91,9 +95,9 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
   const int w_first = pos0 + i0 + warp * 16, w_last = min(w_first + 15, last_pos);    // positions of the warp's rows
   const int w_lo = window > 0 ? w_first - window + 1 : 0;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  float o[D / 8][4];
+  float o[DV / 8][4];
 #pragma unroll
-  for (int j = 0; j < D / 8; ++j)
+  for (int j = 0; j < DV / 8; ++j)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
 
@@ -105,9 +109,16 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
       const int kt = k0 + j;
       const bool ok = kt <= last_pos;
       const int kk = ok ? kt : k0;
-      const int64_t at = (((int64_t)bt[kk / page_size] * G + g) * page_size + kk % page_size) * D + cc * 8;
+      const int64_t at = (((int64_t)bt[kk / page_size] * G + g) * page_size + kk % page_size) * dim + cc * 8;
       cp16(Ks + j * LD + cc * 8, k_pool + at, ok ? 16 : 0);
-      cp16(Vs + j * LD + cc * 8, v_pool + at, ok ? 16 : 0);
+    }
+    for (int c = tid; c < kKeys * CHV; c += 128) {
+      const int j = c / CHV, cc = c - j * CHV;
+      const int kt = k0 + j;
+      const bool ok = kt <= last_pos;
+      const int kk = ok ? kt : k0;
+      const int64_t at = (((int64_t)bt[kk / page_size] * G + g) * page_size + kk % page_size) * DV + cc * 8;
+      cp16(Vs + j * LDV + cc * 8, v_pool + at, ok ? 16 : 0);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -121,7 +132,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
 #pragma unroll
-    for (int kk = 0; kk < D; kk += 16) {
+    for (int kk = 0; kk < dim; kk += 16) {
       uint32_t a[4];
       ldsm4(a, Qs + (warp * 16 + (lane & 15)) * LD + kk + (lane >> 4) * 8);
 #pragma unroll
@@ -173,7 +184,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
       l[u] = l[u] * corr[u] + sum[u];
     }
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
+    for (int j = 0; j < DV / 8; ++j) {
       o[j][0] *= corr[0]; o[j][1] *= corr[0]; o[j][2] *= corr[1]; o[j][3] *= corr[1];
     }
     // ---- O += P V
@@ -182,9 +193,9 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
       uint32_t a[4] = {pack_bf16(s[2 * t][0], s[2 * t][1]), pack_bf16(s[2 * t][2], s[2 * t][3]),
                        pack_bf16(s[2 * t + 1][0], s[2 * t + 1][1]), pack_bf16(s[2 * t + 1][2], s[2 * t + 1][3])};
 #pragma unroll
-      for (int j = 0; j < D / 16; ++j) {
+      for (int j = 0; j < DV / 16; ++j) {
         uint32_t b[4];
-        ldsm4_t(b, Vs + (16 * t + (lane & 15)) * LD + 16 * j + (lane >> 4) * 8);
+        ldsm4_t(b, Vs + (16 * t + (lane & 15)) * LDV + 16 * j + (lane >> 4) * 8);
         mma16816(o[2 * j], a, b[0], b[1]);
         mma16816(o[2 * j + 1], a, b[2], b[3]);
       }
@@ -200,9 +211,9 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
       const float corr = expf(m[u] - m_new);
       inv = corr / (l[u] * corr + expf(sk - m_new));
     }
-    const int64_t base = ((row0 + i0 + my_row[u]) * H + h) * D;
+    const int64_t base = ((row0 + i0 + my_row[u]) * H + h) * DV;
 #pragma unroll
-    for (int j = 0; j < D / 8; ++j) {
+    for (int j = 0; j < DV / 8; ++j) {
       const int c = 8 * j + (lane & 3) * 2;
       const float v0 = o[j][2 * u] * inv, v1 = o[j][2 * u + 1] * inv;
       if constexpr (OUT_BF16) {
@@ -215,36 +226,48 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const bf16* __restrict__ 
   }
 }
 
-template <int D, bool OUT_BF16>
+template <int D, int DV, bool OUT_BF16>
 int launch_mma(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H, int G,
-               float scale, int window, int keep_first, float softcap, const float* sink, void* out, cudaStream_t st) {
-  const size_t smem = (size_t)(kRows + 2 * kKeys) * (D + kPadH) * sizeof(bf16);
+               int dim, float scale, int window, int keep_first, float softcap, const float* sink, void* out, cudaStream_t st) {
+  const size_t smem = ((size_t)(kRows + kKeys) * (dim + kPadH) + (size_t)kKeys * (DV + kPadH)) * sizeof(bf16);
   static SmemAttr attr = {};
-  if (smem > 48 * 1024) PRL_CUDA(ensure_smem(attn_mma_kernel<D, OUT_BF16>, (int)smem, attr));
+  if (smem > 48 * 1024) PRL_CUDA(ensure_smem(attn_mma_kernel<D, DV, OUT_BF16>, (int)smem, attr));
   dim3 grid((max_q + kRows - 1) / kRows, H, n_seg);
-  PRL_CUDA(launch_pdl((attn_mma_kernel<D, OUT_BF16>), grid, dim3(128), smem, st, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt,
-                      max_blocks, page_size, ss, sl, sp, sslot, H, G, scale, window, keep_first, softcap, sink, out));
+  PRL_CUDA(launch_pdl((attn_mma_kernel<D, DV, OUT_BF16>), grid, dim3(128), smem, st, (const bf16*)q, (const bf16*)kp, (const bf16*)vp, bt,
+                      max_blocks, page_size, ss, sl, sp, sslot, H, G, dim, scale, window, keep_first, softcap, sink, out));
   PRL_LAUNCH_CHECK();
   return PRL_OK;
 }
 
 }  // namespace
 
-// bf16 cache and queries with these head sizes take the tensor-core kernel
+// bf16 cache and queries take the tensor-core kernel when the key size is a multiple of 16 up to 256 and the value size
+// one of 16 / 32 / 48 / 64 / 96 / 128 (the square geometries 32, 64, 128 with a fully unrolled score loop)
 bool attn_mma_fits(int dim, int vdim, const void* q, const void* k_pool, const void* v_pool) {
-  return dim == vdim && (dim == 32 || dim == 64 || dim == 128) && (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
+  const bool vok = vdim == 16 || vdim == 32 || vdim == 48 || vdim == 64 || vdim == 96 || vdim == 128;
+  return dim >= 16 && dim % 16 == 0 && dim <= 256 && vok && (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0;
 }
 
 int attn_mma_launch(const void* q, const void* kp, const void* vp, const int32_t* bt, int max_blocks, int page_size,
                     const int32_t* ss, const int32_t* sl, const int32_t* sp, const int32_t* sslot, int n_seg, int max_q, int H,
-                    int G, int dim, float scale, int window, int keep_first, float softcap, const float* sink, int out_is_bf16,
-                    void* out, cudaStream_t st) {
-#define PRL_MMA(D) (out_is_bf16 ? launch_mma<D, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, sink, out, st) \
-                                : launch_mma<D, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, scale, window, keep_first, softcap, sink, out, st))
-  if (dim == 32) return PRL_MMA(32);
-  if (dim == 64) return PRL_MMA(64);
-  return PRL_MMA(128);
+                    int G, int dim, int vdim, float scale, int window, int keep_first, float softcap, const float* sink,
+                    int out_is_bf16, void* out, cudaStream_t st) {
+#define PRL_MMA(D, DV) (out_is_bf16 ? launch_mma<D, DV, true>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, scale, window, keep_first, softcap, sink, out, st) \
+                                    : launch_mma<D, DV, false>(q, kp, vp, bt, max_blocks, page_size, ss, sl, sp, sslot, n_seg, max_q, H, G, dim, scale, window, keep_first, softcap, sink, out, st))
+  if (dim == vdim) {
+    if (dim == 32) return PRL_MMA(32, 32);
+    if (dim == 64) return PRL_MMA(64, 64);
+    if (dim == 128) return PRL_MMA(128, 128);
+  }
+  switch (vdim) {
+    case 16: return PRL_MMA(0, 16);
+    case 32: return PRL_MMA(0, 32);
+    case 48: return PRL_MMA(0, 48);
+    case 64: return PRL_MMA(0, 64);
+    case 96: return PRL_MMA(0, 96);
+    default: return PRL_MMA(0, 128);
+  }
 #undef PRL_MMA
 }
 

@@ -386,13 +386,14 @@ def test_trace_runner_command_line(cuda_device, tmp_path):
             assert got.shape == ref.shape and kc.rel_err(got, ref) < tol
 
 
-@pytest.mark.parametrize("dim,window", [(32, 100), (64, 64), (128, 37)])
-def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, window):
-    """bf16 with head sizes the tensor-core prompt kernel is built for: the sink joins its denominator after the last key
-    tile.  Strong sinks and peaked scores over five page borders, against the CUDA-core kernel on the same cache (they
+@pytest.mark.parametrize("dim,vdim,window", [(32, 32, 100), (64, 64, 64), (128, 128, 37), (80, 48, 90), (48, 96, 33), (16, 16, 200),
+                                             (240, 128, 70)])
+def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, vdim, window):
+    """bf16 with head sizes the tensor-core prompt kernel is built for (square ones and key sizes that differ from the
+    value size): the sink joins its denominator after the last key tile.  Strong sinks and peaked scores over five page borders, against the CUDA-core kernel on the same cache (they
     differ by the bf16 rounding of the softmax weights) and against the oracle; then the latent layer's tensor-core
     kernel with its window, portions and single tokens."""
-    config = kc.model([A(heads=4, kv_heads=2, dim=dim, vdim=dim, rot_dims=dim // 2, window=window, scale=2.0 * dim ** -0.5),
+    config = kc.model([A(heads=4, kv_heads=2, dim=dim, vdim=vdim, rot_dims=dim // 2, window=window, scale=2.0 * dim ** -0.5),
                        T(heads=6, dim=16, rot_dim=16, vdim=24, kv_rank=32, window=window, scale=0.6)], width=64)
     wt = kc.weights(config, 9)
     wt["l0.mix.sink"] = kc.bf16_round(wt["l0.mix.sink"] * 2.0 + 3.0)
