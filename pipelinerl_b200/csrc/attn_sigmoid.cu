@@ -7,8 +7,8 @@
 //     o_h(i)     = sum_j m_h(i, j) v_c(h)(j)                       c(h) = h / (H / G)
 //
 // The mixing couples all heads of a (query, key) pair, so a CTA owns RQ query rows of one segment with ALL their heads.
-// It streams the sequence's keys and values in tiles of 32 (all G key/value heads, converted to fp32) through shared
-// memory.  Per tile: (1) every (row, head) scores the 32 keys, one key per lane, and stores the sigmoid weights;
+// It streams the sequence's keys and values in tiles of 32 (all G key/value heads at once, or one at a time when they
+// do not fit; converted to fp32) through shared memory.  Per tile: (1) every (row, head) scores the 32 keys, one key per lane, and stores the sigmoid weights;
 // (2) the weights are mixed over the heads; (3) every (row, head) adds the tile's weighted values to its accumulator,
 // which lives in shared memory ([RQ][H][vdim] fp32) because the head count is a run-time number.  The eight warps of
 // a CTA are split evenly over the RQ rows; the warps of a row take its heads in turn.  RQ is chosen at launch
@@ -22,7 +22,8 @@
 // weights to shared memory ([H][16][32] fp32); (2) every warp mixes the weights of its own output heads (a dot product
 // over the source heads per element, read in the A-operand layout of the next product) and rounds them to bf16;
 // (3) O += M V on the tensor cores, the accumulators of the warp's output heads in registers.  More output heads than
-// eight warps hold are split over CTAs that repeat the scores.  A batch of short segments (a decode step) spreads the
+// eight warps hold are split over CTAs that repeat the scores.  When the queries of all heads do not fit in shared memory
+// beside the tiles (32 heads of 128), their fragments are read from L2 in every tile instead.  A batch of short segments (a decode step) spreads the
 // key tiles of a segment over several CTAs: nothing is normalised, so their shares are simply added, by a second
 // launch in a fixed order.
 //
@@ -59,9 +60,10 @@ struct SigmoidAttnArgs {
   const float* talk;
   int rq;
   void* out;
+  int kv_stage;          // CUDA-core kernel: key / value heads staged at a time (G, or 1 when all of them do not fit)
 };
 
-__host__ __device__ inline size_t sigmoid_attn_floats(int rq, int H, int G, int dim, int vdim) {
+__host__ __device__ inline size_t sigmoid_attn_floats(int rq, int H, int G, int dim, int vdim) {   // G: heads staged at a time
   return (size_t)rq * H * dim + (size_t)G * kKeys * (dim + 1) + (size_t)G * kKeys * vdim + 2 * (size_t)rq * H * kKeys +
          (size_t)rq * H * vdim + (size_t)H * H + H + rq;
 }
@@ -75,10 +77,11 @@ __global__ void __launch_bounds__(32 * kWarps) attn_sigmoid_kernel(SigmoidAttnAr
   const int i0 = blockIdx.x * RQ;
   if (i0 >= len) return;
   const int H = a.H, G = a.G, dim = a.dim, vdim = a.vdim, dimp = dim + 1;
+  const int GS = a.kv_stage;                        // key / value heads in shared memory at a time
   float* qs = sm;                                   // [RQ][H][dim]
-  float* ks = qs + (size_t)RQ * H * dim;            // [G][32][dim + 1]
-  float* vs = ks + (size_t)G * kKeys * dimp;        // [G][32][vdim]
-  float* wt = vs + (size_t)G * kKeys * vdim;        // [RQ][H][32] sigmoid weights
+  float* ks = qs + (size_t)RQ * H * dim;            // [GS][32][dim + 1]
+  float* vs = ks + (size_t)GS * kKeys * dimp;       // [GS][32][vdim]
+  float* wt = vs + (size_t)GS * kKeys * vdim;       // [RQ][H][32] sigmoid weights
   float* mx = wt + (size_t)RQ * H * kKeys;          // [RQ][H][32] mixed weights
   float* acc = mx + (size_t)RQ * H * kKeys;         // [RQ][H][vdim]
   float* tk = acc + (size_t)RQ * H * vdim;          // [H][H]
@@ -112,31 +115,29 @@ __global__ void __launch_bounds__(32 * kWarps) attn_sigmoid_kernel(SigmoidAttnAr
   const int n_tiles = last_pos / kKeys + 1;
   for (int kt = 0; kt < n_tiles; ++kt) {
     const int k0 = kt * kKeys;
-    __syncthreads();                                // the previous tile's readers are done (and the setup above is visible)
     const int page = a.block_table[(int64_t)slot * a.max_blocks + k0 / a.page_size];
     const int in_page = k0 % a.page_size;
-    for (int e = tid; e < G * kKeys * dim; e += blockDim.x) {
-      const int g = e / (kKeys * dim), rest = e - g * kKeys * dim, j = rest / dim, d = rest - j * dim;
-      ks[((size_t)g * kKeys + j) * dimp + d] =
-          k0 + j <= last_pos ? cvt(k_pool[(((int64_t)page * G + g) * a.page_size + in_page + j) * dim + d]) : 0.f;
-    }
-    for (int e = tid; e < G * kKeys * vdim; e += blockDim.x) {
-      const int g = e / (kKeys * vdim), rest = e - g * kKeys * vdim, j = rest / vdim;
-      vs[e] = k0 + j <= last_pos ? cvt(v_pool[(((int64_t)page * G + g) * a.page_size + in_page) * vdim + rest]) : 0.f;
-    }
-    __syncthreads();
-    // (1) weights: lane = key
     const bool seen = r < rows && k0 + lane <= my_pos;
-    for (int h = sub; h < H; h += wpr) {
-      const float* qh = qs + ((size_t)r * H + h) * dim;
-      const float* kj = ks + ((size_t)(h / rep) * kKeys + lane) * dimp;
-      float s0 = 0.f, s1 = 0.f;
-      int d = 0;
-      for (; d + 1 < dim; d += 2) { s0 = fmaf(qh[d], kj[d], s0); s1 = fmaf(qh[d + 1], kj[d + 1], s1); }
-      if (d < dim) s0 = fmaf(qh[d], kj[d], s0);
-      float s = (s0 + s1) * srow[r];
-      if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-      wt[((size_t)r * H + h) * kKeys + lane] = seen ? 1.f / (1.f + expf(-(s + pb[h]))) : 0.f;
+    // (1) weights, the key heads staged GS at a time: lane = key
+    for (int c0 = 0; c0 < G; c0 += GS) {
+      __syncthreads();                              // the previous readers of ks are done (and the setup above is visible)
+      for (int e = tid; e < GS * kKeys * dim; e += blockDim.x) {
+        const int g = e / (kKeys * dim), rest = e - g * kKeys * dim, j = rest / dim, d = rest - j * dim;
+        ks[((size_t)g * kKeys + j) * dimp + d] =
+            k0 + j <= last_pos ? cvt(k_pool[(((int64_t)page * G + c0 + g) * a.page_size + in_page + j) * dim + d]) : 0.f;
+      }
+      __syncthreads();
+      for (int h = c0 * rep + sub; h < (c0 + GS) * rep; h += wpr) {
+        const float* qh = qs + ((size_t)r * H + h) * dim;
+        const float* kj = ks + ((size_t)(h / rep - c0) * kKeys + lane) * dimp;
+        float s0 = 0.f, s1 = 0.f;
+        int d = 0;
+        for (; d + 1 < dim; d += 2) { s0 = fmaf(qh[d], kj[d], s0); s1 = fmaf(qh[d + 1], kj[d + 1], s1); }
+        if (d < dim) s0 = fmaf(qh[d], kj[d], s0);
+        float s = (s0 + s1) * srow[r];
+        if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+        wt[((size_t)r * H + h) * kKeys + lane] = seen ? 1.f / (1.f + expf(-(s + pb[h]))) : 0.f;
+      }
     }
     __syncthreads();
     // (2) mix over the heads
@@ -145,18 +146,25 @@ __global__ void __launch_bounds__(32 * kWarps) attn_sigmoid_kernel(SigmoidAttnAr
       for (int g = 0; g < H; ++g) m = fmaf(tk[h * H + g], wt[((size_t)r * H + g) * kKeys + lane], m);
       mx[((size_t)r * H + h) * kKeys + lane] = m;
     }
-    __syncthreads();
-    // (3) weighted values: lane = value channel
-    if (r < rows) {
-      const int nk = min(kKeys, my_pos - k0 + 1);   // keys of this tile the row sees (<= 0: none)
-      for (int h = sub; h < H; h += wpr) {
-        const float* mh = mx + ((size_t)r * H + h) * kKeys;
-        const float* vh = vs + (size_t)(h / rep) * kKeys * vdim;
-        float* ah = acc + ((size_t)r * H + h) * vdim;
-        for (int e = lane; e < vdim; e += 32) {
-          float o = ah[e];
-          for (int j = 0; j < nk; ++j) o = fmaf(mh[j], vh[j * vdim + e], o);
-          ah[e] = o;
+    // (3) weighted values, the value heads staged likewise: lane = value channel
+    const int nk = min(kKeys, my_pos - k0 + 1);     // keys of this tile the row sees (<= 0: none)
+    for (int c0 = 0; c0 < G; c0 += GS) {
+      __syncthreads();                              // mx is written; the previous readers of vs are done
+      for (int e = tid; e < GS * kKeys * vdim; e += blockDim.x) {
+        const int g = e / (kKeys * vdim), rest = e - g * kKeys * vdim, j = rest / vdim;
+        vs[e] = k0 + j <= last_pos ? cvt(v_pool[(((int64_t)page * G + c0 + g) * a.page_size + in_page) * vdim + rest]) : 0.f;
+      }
+      __syncthreads();
+      if (r < rows) {
+        for (int h = c0 * rep + sub; h < (c0 + GS) * rep; h += wpr) {
+          const float* mh = mx + ((size_t)r * H + h) * kKeys;
+          const float* vh = vs + (size_t)(h / rep - c0) * kKeys * vdim;
+          float* ah = acc + ((size_t)r * H + h) * vdim;
+          for (int e = lane; e < vdim; e += 32) {
+            float o = ah[e];
+            for (int j = 0; j < nk; ++j) o = fmaf(mh[j], vh[j * vdim + e], o);
+            ah[e] = o;
+          }
         }
       }
     }
@@ -203,10 +211,11 @@ struct SigmoidTcArgs {
   int splits;            // CTAs that share the key tiles of a row tile (their shares go to ws and are added afterwards)
   int64_t n_rows;        // rows of the batch: the stride between the splits' shares in ws
   float* ws;             // [splits][n_rows][H][vdim] fp32 when splits > 1
+  int q_global;          // the queries of all heads do not fit in shared memory beside the tiles: their fragments come from L2
 };
 
-__host__ __device__ inline size_t sigmoid_tc_smem(int H, int G, int dim, int vdim) {
-  return ((size_t)kTcRows * (H * dim + kPadH) + (size_t)G * kKeys * (dim + kPadH) + (size_t)G * kKeys * (vdim + kPadH)) * sizeof(bf16) +
+__host__ __device__ inline size_t sigmoid_tc_smem(int H, int G, int dim, int vdim, bool q_staged = true) {
+  return ((q_staged ? (size_t)kTcRows * (H * dim + kPadH) : 0) + (size_t)G * kKeys * (dim + kPadH) + (size_t)G * kKeys * (vdim + kPadH)) * sizeof(bf16) +
          ((size_t)H * kTcRows * kWtLd + (size_t)H * H + H + kTcRows) * sizeof(float);
 }
 
@@ -228,7 +237,7 @@ __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(Sigmo
   constexpr int vdim = NV * 8;
   const int ldq = H * dim + kPadH, ldk = dim + kPadH, ldv = vdim + kPadH;
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [16][ldq]: all heads of the CTA's rows
-  bf16* Ks = Qs + kTcRows * ldq;                                // [G][32][ldk]
+  bf16* Ks = Qs + (ta.q_global ? 0 : kTcRows * ldq);            // [G][32][ldk]
   bf16* Vs = Ks + (size_t)G * kKeys * ldk;                      // [G][32][ldv]
   float* Wt = reinterpret_cast<float*>(Vs + (size_t)G * kKeys * ldv);   // [H][16][kWtLd] sigmoid weights of the tile
   float* tk = Wt + (size_t)H * kTcRows * kWtLd;                 // [H][H]
@@ -247,7 +256,7 @@ __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(Sigmo
   const int per = (tiles_total + ta.splits - 1) / ta.splits;
   const int t_begin = split * per, t_end = min(tiles_total, t_begin + per);
 
-  const int chq = H * dim / 8;
+  const int chq = ta.q_global ? 0 : H * dim / 8;
   for (int c = tid; c < kTcRows * chq; c += blockDim.x) {
     const int r = c / chq, cc = c - r * chq;
     const bool ok = r < rows;
@@ -316,10 +325,21 @@ __global__ void __launch_bounds__(32 * kTcWarps, 1) attn_sigmoid_tc_kernel(Sigmo
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
       const bf16* qa = Qs + (lane & 15) * ldq + g * dim + (lane >> 4) * 8;
+      // without staged queries: the A fragment's four registers straight from the query rows (rows gid, gid + 8; the
+      // row past the segment's end reads row 0 and is masked below)
+      const bf16* qg0 = q + ((row0 + i0 + (gid < rows ? gid : 0)) * H + g) * dim + t2;
+      const bf16* qg1 = q + ((row0 + i0 + (gid + 8 < rows ? gid + 8 : 0)) * H + g) * dim + t2;
       const bf16* kb = Ks + ((size_t)(g / rep) * kKeys + ((lane >> 4) << 3) + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
       for (int c = 0; c < dim; c += 16) {
         uint32_t af[4], b01[4], b23[4];
-        ldsm4(af, qa + c);
+        if (ta.q_global) {
+          af[0] = *reinterpret_cast<const uint32_t*>(qg0 + c);
+          af[1] = *reinterpret_cast<const uint32_t*>(qg1 + c);
+          af[2] = *reinterpret_cast<const uint32_t*>(qg0 + c + 8);
+          af[3] = *reinterpret_cast<const uint32_t*>(qg1 + c + 8);
+        } else {
+          ldsm4(af, qa + c);
+        }
         ldsm4(b01, kb + c);                 // keys 0..15: (b0, b1) of n-tile 0, (b0, b1) of n-tile 1
         ldsm4(b23, kb + 16 * ldk + c);      // keys 16..31
         mma16816(s[0], af, b01[0], b01[1]);
@@ -443,7 +463,7 @@ using namespace prl;
 // 1 if the tensor-core kernel runs this geometry in bf16 (else prl_attn_sigmoid takes the CUDA-core kernel)
 extern "C" int32_t prl_attn_sigmoid_tc_fits(int32_t H, int32_t G, int32_t dim, int32_t vdim) {
   return H >= 1 && G >= 1 && H % G == 0 && dim >= 16 && dim % 16 == 0 && vdim >= 16 && vdim % 16 == 0 && vdim <= 128 &&
-         sigmoid_tc_smem(H, G, dim, vdim) <= 200 * 1024;
+         sigmoid_tc_smem(H, G, dim, vdim, false) <= 226 * 1024;
 }
 
 // CTAs that share the key tiles of a row tile when the batch has fewer row tiles than the GPU has SMs (a decode step, a
@@ -483,9 +503,10 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
     int splits = sigmoid_splits(n_seg, max_q, H, vdim);
     if (!ws || n_rows < 1 || ws_bytes < prl_attn_sigmoid_workspace_bytes(n_rows, n_seg, max_q, H, vdim)) splits = 1;
     SigmoidTcArgs ta{{q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot,
-                      H, G, dim, vdim, scale, softcap, temp_coef, temp_every, head_bias, talk, 0, out},
-                     splits, (int64_t)n_rows, (float*)ws};
-    const size_t smem = sigmoid_tc_smem(H, G, dim, vdim);
+                      H, G, dim, vdim, scale, softcap, temp_coef, temp_every, head_bias, talk, 0, out, G},
+                     splits, (int64_t)n_rows, (float*)ws, 0};
+    ta.q_global = sigmoid_tc_smem(H, G, dim, vdim) > 200 * 1024;
+    const size_t smem = sigmoid_tc_smem(H, G, dim, vdim, !ta.q_global);
     dim3 grid((max_q + kTcRows - 1) / kTcRows, n_seg, splits * groups);
     static SmemAttr attr[8] = {};
 #define PRL_SIGTC(NV)                                                                                               \
@@ -510,10 +531,17 @@ extern "C" int prl_attn_sigmoid(const void* q, const void* k_pool, const void* v
   while (rq > 1 && rq / 2 >= max_q) rq /= 2;                                   // short segments: more warps per row
   const size_t budget = 200 * 1024;
   while (rq > 1 && sigmoid_attn_floats(rq, H, G, dim, vdim) * sizeof(float) > budget) rq /= 2;
-  const size_t smem = sigmoid_attn_floats(rq, H, G, dim, vdim) * sizeof(float);
+  int kv_stage = G;                                 // all key / value heads of a tile at once, or one at a time
+  if (sigmoid_attn_floats(rq, H, G, dim, vdim) * sizeof(float) > budget) {
+    kv_stage = 1;
+    rq = 8;
+    while (rq > 1 && rq / 2 >= max_q) rq /= 2;
+    while (rq > 1 && sigmoid_attn_floats(rq, H, 1, dim, vdim) * sizeof(float) > budget) rq /= 2;
+  }
+  const size_t smem = sigmoid_attn_floats(rq, H, kv_stage, dim, vdim) * sizeof(float);
   PRL_CHECK_ARG(smem <= budget, "prl_attn_sigmoid: %d heads of %d + %d channels do not fit in shared memory", H, dim, vdim);
   SigmoidAttnArgs a{q, k_pool, v_pool, block_table, max_blocks, page_size, seg_start, seg_len, seg_pos0, seg_slot,
-                    H, G, dim, vdim, scale, softcap, temp_coef, temp_every, head_bias, talk, rq, out};
+                    H, G, dim, vdim, scale, softcap, temp_coef, temp_every, head_bias, talk, rq, out, kv_stage};
   dim3 grid((max_q + rq - 1) / rq, n_seg);
   static SmemAttr attr[3] = {};
 #define PRL_SIG(T, TOUT, I)                                                                        \

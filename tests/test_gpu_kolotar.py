@@ -415,9 +415,10 @@ def test_tensor_core_prompt_attention_with_sink_and_window(cuda_device, dim, vdi
 
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 32, 32), (6, 3, 16, 64), (20, 4, 16, 128), (3, 1, 48, 128), (6, 2, 80, 48),
-                                                      (2, 2, 16, 16), (5, 5, 32, 112)])
+                                                      (2, 2, 16, 16), (5, 5, 32, 112), (32, 8, 128, 128)])
 def test_tensor_core_attention_without_a_softmax(cuda_device, heads, kv_heads, dim, vdim):
-    """bf16 with sizes the tensor-core kernel is built for (more output heads than one CTA holds in one case): prompt
+    """bf16 with sizes the tensor-core kernel is built for (more output heads than one CTA holds in two cases, of which the
+    last has queries too large to be staged beside the tiles): prompt
     portions, mixed batches and single tokens (whose keys are split over CTAs and added afterwards) against the
     CUDA-core kernel on the same cache (they differ by the bf16 rounding of the mixed weights) and against the oracle.
     Weights kept small by the head bias so that 330 unnormalised terms stay O(1)."""
