@@ -489,8 +489,9 @@ class HybridConfig:
                     raise ValueError(f"layer run {i}: bad router {L.mlp.moe}")
                 if L.kind == "latent_attention":
                     a = L.latent
-                    if a.rot_dim % 2 or a.kv_rank + a.rot_dim > 1024 or min(a.heads, a.dim, a.vdim, a.kv_rank) < 1 or a.q_rank or a.window < 0:
-                        raise ValueError(f"layer run {i}: bad latent-attention geometry {a}")
+                    if (a.rot_dim % 2 or a.kv_rank > 512 or a.kv_rank + a.rot_dim > 1024 or min(a.heads, a.dim, a.vdim, a.kv_rank) < 1
+                            or a.q_rank or a.window < 0):
+                        raise ValueError(f"layer run {i}: bad latent-attention geometry {a} (kv_rank <= 512, even rot_dim)")
                     continue
                 a = L.attn
                 if a.heads % a.kv_heads or a.rot_dims % 2 or a.rot_dims > a.dim or a.dim > 1024 or a.vdim > 512 or a.window < 0:
